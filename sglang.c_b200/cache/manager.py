@@ -24,7 +24,7 @@ class _Group:
     need: CacheNeed
     calls: List[int]                 # indices into the running order that own a cache here
     pool: Optional[PagePool] = None  # paged_kv only
-    tensor: object = None            # [n_calls, n_pages, 2, Hkv, page_size, D] or [n_calls, n_slots, *shape]
+    tensor: object = None            # [n_calls, n_pages, 2 (1: shared), Hkv, page_size, D] or [n_calls, n_slots, *shape]
     tables: Dict[object, List[int]] = field(default_factory=dict)   # request -> page per block (-1 = released)
 
 
@@ -59,7 +59,8 @@ class CacheManager:
         for g in self.groups:
             if g.need.kind == "paged_kv":
                 g.pool = PagePool(self.n_pages)
-                shape = (len(g.calls), self.n_pages, 2, g.need.n_kv_heads, self.page_size, g.need.head_dim)
+                shape = (len(g.calls), self.n_pages, 1 if g.need.shared else 2, g.need.n_kv_heads, self.page_size,
+                         g.need.head_dim)
                 dt = cache_dtype
             elif g.need.kind == "state":
                 shape = (len(g.calls), self.max_requests) + tuple(g.need.state_shape)

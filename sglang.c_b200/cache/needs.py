@@ -8,19 +8,23 @@ class CacheNeed:
     """kind "paged_kv": keys and values of every position (or of the last
     `window` positions) in pages; kind "state": one block of fixed shape per
     request.  Calls whose needs are equal share a group: one page id (or slot
-    id) is valid in all of them."""
+    id) is valid in all of them.  `shared` (paged_kv): a position keeps ONE row
+    per head that is read as key and as value (a latent from which a mixer makes
+    both), so a page holds half as much."""
     kind: str
     n_kv_heads: int = 0
     head_dim: int = 0
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
+    shared: bool = False
 
     @classmethod
-    def paged_kv(cls, n_kv_heads, head_dim, window=None):
+    def paged_kv(cls, n_kv_heads, head_dim, window=None, shared=False):
         if window is not None and window <= 0:
             raise ValueError("window must be a positive count of keys or None")
-        return cls("paged_kv", int(n_kv_heads), int(head_dim), None if window is None else int(window))
+        return cls("paged_kv", int(n_kv_heads), int(head_dim), None if window is None else int(window),
+                   shared=bool(shared))
 
     @classmethod
     def state(cls, shape, dtype="float32"):
@@ -31,7 +35,8 @@ class CacheNeed:
 class CacheBinding:
     """What a mixer call gets: its own tensor and the group whose block tables
     (or slot ids) index it.  paged_kv: tensor [n_pages, 2, n_kv_heads,
-    page_size, head_dim]; state: tensor [n_slots, *state_shape].  `write` is
+    page_size, head_dim] ([n_pages, 1, ...] for a shared need); state: tensor
+    [n_slots, *state_shape].  `write` is
     false for a call that reads the cache another call wrote."""
     kind: str
     group: int

@@ -1,8 +1,9 @@
 from .base import ConfigError, read_config_json
 from .gpt2 import GPT2Config
+from .tukavik import TukavikConfig, TukavikLayer
 from .registry import (Architecture, known_architectures, load_config,
                        register_architecture, resolve_architecture)
 
-__all__ = ["ConfigError", "read_config_json", "GPT2Config", "Architecture",
+__all__ = ["ConfigError", "read_config_json", "GPT2Config", "TukavikConfig", "TukavikLayer", "Architecture",
            "known_architectures", "load_config", "register_architecture",
            "resolve_architecture"]

@@ -3,7 +3,7 @@ its model plan.
 
 The reference decides by which keys config.json holds (src/model.c:24-41) and
 its GPU command line by `model_type` (apps/cuda_cli.c:25-36).  Here the first
-entry of `architectures` decides, `model_type` is the fallback, and an unknown
+entry of `architectures` (or the one name under `architecture`) decides, `model_type` is the fallback, and an unknown
 name is an error that lists the known ones.
 """
 from dataclasses import dataclass
@@ -43,7 +43,7 @@ def _load_builtin():
 
 def resolve_architecture(config_dict):
     _load_builtin()
-    names = config_dict.get("architectures") or []
+    names = config_dict.get("architectures") or config_dict.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for n in names:

@@ -36,7 +36,7 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
                       const int* __restrict__ block_table, int bt_stride,
                       const int* __restrict__ token_req, const int* __restrict__ positions,
                       TO* __restrict__ out, int o_stride, int T, int H, int Hkv, int D, int page_size,
-                      float scale, int window, int n_pages, int* err) {
+                      float scale, int window, int n_pages, int* err, int kv_shared) {
   extern __shared__ __align__(16) float smem[];
   __shared__ int s_req[W], s_lo[W], s_pos[W];
   // padded key rows: a lane a key without bank conflicts (by 4 where rows are read 16 bytes at a time)
@@ -68,8 +68,9 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
   float acc[8];                               // dims lane, lane + 32, ... of the output
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-  const size_t page_elems = (size_t)2 * Hkv * page_size * D;
-  const size_t head_off = (size_t)hk * page_size * D, v_off = (size_t)Hkv * page_size * D;
+  // kv_shared: a page holds one block of rows that are keys and values at once (a latent)
+  const size_t page_elems = (size_t)(kv_shared ? 1 : 2) * Hkv * page_size * D;
+  const size_t head_off = (size_t)hk * page_size * D, v_off = kv_shared ? 0 : (size_t)Hkv * page_size * D;
 
   // The tokens of a block that belong to one request (a run: a request's tokens lie together)
   // share the tiles of that request's keys and values; the runs of a block take turns.
@@ -179,12 +180,12 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
 // sees.  q/out dtype = act_dtype, cache dtype = cache_dtype.  n_pages and err serve the
 // bounds-check build (page ids are compared with n_pages; err gets the flag).  max_q_len: the
 // longest portion of the step (1: every request brings one token, and a block takes one token).
-SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
-                                 const int* block_table, int bt_stride, const int* token_req,
-                                 const int* positions, void* out, int o_stride, int T, int H,
-                                 int Hkv, int D, int page_size, float scale, int window,
-                                 int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
-                                 int max_q_len, cudaStream_t stream) {
+static int attention_simt_run(const void* q, int q_stride, const void* cache,
+                              const int* block_table, int bt_stride, const int* token_req,
+                              const int* positions, void* out, int o_stride, int T, int H,
+                              int Hkv, int D, int page_size, float scale, int window,
+                              int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
+                              int max_q_len, int kv_shared, cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || page_size <= 0 || max_keys <= 0)
     return SGLC_ERR_ARGUMENT;
@@ -201,7 +202,7 @@ SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                    \
     attention_simt_kernel<TQ, TC, TO, WW, TH><<<grid, TH, smem, stream>>>(                              \
         (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions,        \
-        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err);                     \
+        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err, kv_shared);          \
   } while (0)
   if (act_dtype == SGLC_F32 && cache_dtype == SGLC_F32) {
     if (single) LAUNCH(float, float, float, 1, 128);
@@ -214,4 +215,28 @@ SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
   }
 #undef LAUNCH
   return sglc_launch_status();
+}
+
+SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
+                                 const int* block_table, int bt_stride, const int* token_req,
+                                 const int* positions, void* out, int o_stride, int T, int H,
+                                 int Hkv, int D, int page_size, float scale, int window,
+                                 int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
+                                 int max_q_len, cudaStream_t stream) {
+  return attention_simt_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride,
+                            T, H, Hkv, D, page_size, scale, window, max_keys, act_dtype, cache_dtype,
+                            n_pages, err, max_q_len, 0, stream);
+}
+
+// The same over a cache whose pages hold one block of rows [Hkv][page_size][D] that serve as keys
+// and as values (attention over a latent that both are read from): cache [n_pages][1][Hkv][page_size][D].
+SGLC_API int sglc_attention_simt_shared(const void* q, int q_stride, const void* cache,
+                                        const int* block_table, int bt_stride, const int* token_req,
+                                        const int* positions, void* out, int o_stride, int T, int H,
+                                        int Hkv, int D, int page_size, float scale, int window,
+                                        int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
+                                        int max_q_len, cudaStream_t stream) {
+  return attention_simt_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride,
+                            T, H, Hkv, D, page_size, scale, window, max_keys, act_dtype, cache_dtype,
+                            n_pages, err, max_q_len, 1, stream);
 }

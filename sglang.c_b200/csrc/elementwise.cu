@@ -1,0 +1,100 @@
+// Element-wise operations on the rows of a step.
+//
+// Depth mix: a model that hands every layer a weighted sum of all earlier layers' results keeps
+// those results for the step's tokens, hist[j] (j = 0: the embedding output; j = i + 1: the
+// result of layer i), as consecutive [n] blocks of 32-bit floats.  After layer i:
+//   hist[i+1] = x;   x = sum_{j=0..i+1} w[j] * hist[j]      (32-bit, j ascending)
+// with n_terms = i + 2.  n_terms = 1 only saves x as hist[0].
+//
+// Activation: y = act(x) for the activations that carry parameters of their own, where the
+// product ahead has no epilogue for them.  xIELU with the two numbers ap > 0, an:
+//   x > 0:   ap x^2 + x/2
+//   x <= 0:  an (exp(x) - 1 - x) + x/2
+#include "common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+// VEC: n is a multiple of 4, so every hist block is 16-byte aligned and four elements go a load
+template <bool VEC>
+__global__ void depth_mix_kernel(float* __restrict__ x, float* __restrict__ hist, long long n,
+                                 int n_terms, const float* __restrict__ w) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long n4 = VEC ? n / 4 : 0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    reinterpret_cast<float4*>(hist + (size_t)(n_terms - 1) * n)[i] = v;
+    if (n_terms > 1) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j < n_terms - 1; j++) {
+        const float4 h = reinterpret_cast<const float4*>(hist + (size_t)j * n)[i];
+        const float wj = w[j];
+        acc.x = fmaf(wj, h.x, acc.x); acc.y = fmaf(wj, h.y, acc.y);
+        acc.z = fmaf(wj, h.z, acc.z); acc.w = fmaf(wj, h.w, acc.w);
+      }
+      const float wl = w[n_terms - 1];
+      acc.x = fmaf(wl, v.x, acc.x); acc.y = fmaf(wl, v.y, acc.y);
+      acc.z = fmaf(wl, v.z, acc.z); acc.w = fmaf(wl, v.w, acc.w);
+      reinterpret_cast<float4*>(x)[i] = acc;
+    }
+  }
+  for (long long i = n4 * 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = x[i];
+    hist[(size_t)(n_terms - 1) * n + i] = v;
+    if (n_terms > 1) {
+      float acc = 0.0f;
+      for (int j = 0; j < n_terms - 1; j++) acc = fmaf(w[j], hist[(size_t)j * n + i], acc);
+      x[i] = fmaf(w[n_terms - 1], v, acc);
+    }
+  }
+}
+
+// x: [n] floats (the step's residual rows); hist: [n_terms and more][n]; w: [n_terms] floats
+SGLC_API int sglc_depth_mix(float* x, float* hist, long long n, int n_terms, const float* w,
+                            cudaStream_t stream) {
+  if (n <= 0) return SGLC_OK;
+  if (n_terms < 1 || (n_terms > 1 && !w)) return SGLC_ERR_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(hist) & 15)) return SGLC_ERR_ARGUMENT;
+  const bool vec = n % 4 == 0;
+  const long long work = vec ? n / 4 : n;
+  int blocks = (int)((work + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (vec) return sglc_launch(depth_mix_kernel<true>, dim3(blocks), dim3(256), 0, stream, 1, true, x, hist, n, n_terms, w);
+  return sglc_launch(depth_mix_kernel<false>, dim3(blocks), dim3(256), 0, stream, 1, true, x, hist, n, n_terms, w);
+}
+
+__device__ __forceinline__ float xielu_f32(float v, float ap, float an) {
+  return v > 0.0f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
+}
+
+template <typename TI, typename TO>
+__global__ void xielu_kernel(const TI* __restrict__ src, long long src_stride, TO* __restrict__ dst,
+                             long long dst_stride, int rows, int cols, float ap, float an) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols, c = i % cols;
+    dst[r * dst_stride + c] = from_f32<TO>(xielu_f32(to_f32(src[r * src_stride + c]), ap, an));
+  }
+}
+
+SGLC_API int sglc_xielu(const void* src, long long src_stride, int src_dtype, void* dst,
+                        long long dst_stride, int dst_dtype, int rows, int cols, float ap, float an,
+                        cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return SGLC_OK;
+  const long long total = (long long)rows * cols;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+#define LAUNCH(TI, TO)                                                                              \
+  return sglc_launch(xielu_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, 1, true, (const TI*)src, \
+                     src_stride, (TO*)dst, dst_stride, rows, cols, ap, an)
+  if (src_dtype == SGLC_F32 && dst_dtype == SGLC_F32) LAUNCH(float, float);
+  if (src_dtype == SGLC_F32 && dst_dtype == SGLC_BF16) LAUNCH(float, __nv_bfloat16);
+  if (src_dtype == SGLC_BF16 && dst_dtype == SGLC_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+  return SGLC_ERR_ARGUMENT;
+}

@@ -79,3 +79,49 @@ SGLC_API int sglc_add_rows(float* x, const int* idx, const void* table, int T, i
     return SGLC_ERR_ARGUMENT;
   return sglc_launch_status();
 }
+
+// Token rows plus a sinusoidal position vector computed on the spot:
+//   x[t, 2i] = wte[tok[t], 2i] + sin(pos[t] * f[i]),   x[t, 2i+1] = wte[tok[t], 2i+1] + cos(pos[t] * f[i])
+// f[i] (the inverse wavelengths, e.g. base^(-2i/E)) comes as a table of doubles made on the host:
+// the angle is formed in 64-bit and brought into one turn there, so that sine and cosine of a
+// position in the thousands are as exact as those of position 1.
+template <typename TW>
+__global__ void embed_sinusoid_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
+                                      const TW* __restrict__ wte, const double* __restrict__ inv_freq,
+                                      float* __restrict__ out, int T, int E, int V, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = tokens[t], pos = positions[t];
+  if (tok < 0 || tok >= V || pos < 0) {
+    if (threadIdx.x == 0 && err) atomicExch(err, 1);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) out[(size_t)t * E + e] = 0.0f;
+    return;
+  }
+  const TW* a = wte + (size_t)tok * E;
+  float* o = out + (size_t)t * E;
+  const double two_pi = 6.283185307179586476925286766559;
+  for (int i = threadIdx.x; 2 * i < E; i += blockDim.x) {
+    double ang = (double)pos * inv_freq[i];
+    ang -= two_pi * floor(ang / two_pi);
+    float s, c;
+    sincosf((float)ang, &s, &c);
+    o[2 * i] = to_f32(a[2 * i]) + s;
+    if (2 * i + 1 < E) o[2 * i + 1] = to_f32(a[2 * i + 1]) + c;
+  }
+}
+
+SGLC_API int sglc_embed_sinusoid(const int* tokens, const int* positions, const void* wte,
+                                 const double* inv_freq, float* out, int T, int E, int V,
+                                 int table_dtype, int* err, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  const int threads = E >= 2048 ? 256 : (E >= 512 ? 128 : 64);
+  if (table_dtype == SGLC_F32)
+    return sglc_launch(embed_sinusoid_kernel<float>, dim3(T), dim3(threads), 0, stream, 1, true, tokens,
+                       positions, (const float*)wte, inv_freq, out, T, E, V, err);
+  if (table_dtype == SGLC_BF16)
+    return sglc_launch(embed_sinusoid_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, 1, true,
+                       tokens, positions, (const __nv_bfloat16*)wte, inv_freq, out, T, E, V, err);
+  return SGLC_ERR_ARGUMENT;
+}

@@ -1,0 +1,96 @@
+// Row norms in their general form, for the places the LayerNorm-with-bias kernel does not cover:
+//   layer form   y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * g (+ b)
+//   RMS form     y = x / sqrt(mean(x^2) + eps) * g (+ b)
+// gain and bias may each be absent.  The source is float or bfloat16 with a free row stride (a
+// column range of a wider buffer: a latent beside the queries of one projection) and an optional
+// row gather; statistics are two-pass in 32-bit.  Three destinations:
+//   rows      dst[r, :] = y                      (float or bfloat16, free row stride)
+//   scatter   dst[dst_rows[r], :] = y            (the rows of a paged cache, by slot)
+//   add       dst[r, :] += y                     (float: a norm behind a sublayer, summed into the
+//                                                 32-bit residual stream)
+// One block a row; the order of a row's additions depends on the row's width only, so a row's
+// bits do not depend on what else is in the step.
+#include "common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+enum { NORM_LAYER = 0, NORM_RMS = 1 };
+
+template <typename TI, typename TO, bool ADD>
+__global__ void norm_rows_kernel(const TI* __restrict__ src, long long src_stride,
+                                 const int* __restrict__ src_rows, const float* __restrict__ gain, const float* __restrict__ bias,
+                                 TO* __restrict__ dst, long long dst_stride, const int* __restrict__ dst_rows,
+                                 int n_rows, int E, float eps, int form, long long dst_row_limit,
+                                 int* __restrict__ err) {
+  extern __shared__ float srow[];   // E floats
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  pdl_launch_dependents();
+  pdl_wait();
+  const TI* xr = src + (size_t)(src_rows ? src_rows[r] : r) * src_stride;
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float v = to_f32(xr[i]);
+    srow[i] = v;
+    s += v;
+  }
+  float mean = 0.0f;
+  if (form == NORM_LAYER) mean = block_sum(s, red) / (float)E;
+  else __syncthreads();
+  float q = 0.0f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float d = srow[i] - mean;
+    q += d * d;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(q, red) / (float)E + eps);
+  long long row = r;
+  if (dst_rows) {
+    row = dst_rows[r];
+    if (row < 0 || !sglc_index_ok(row, dst_row_limit, err)) return;
+  }
+  TO* o = dst + (size_t)row * dst_stride;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    float y = (srow[i] - mean) * inv;
+    if (gain) y *= gain[i];
+    if (bias) y += bias[i];
+    if (ADD) o[i] = from_f32<TO>(to_f32(o[i]) + y);
+    else o[i] = from_f32<TO>(y);
+  }
+}
+
+// form: 0 layer, 1 RMS.  src_rows: null, or the source row of every output row (a gather).  src_dtype/dst_dtype: SGLC_F32 or SGLC_BF16.  dst_rows: null, or the
+// destination row of every source row (negative: the row is skipped); dst_row_limit: rows the
+// destination holds (the bounds-check build compares).  add != 0: dst (float) += y.
+SGLC_API int sglc_norm_rows(const void* src, long long src_stride, int src_dtype, const int* src_rows,
+                            const float* gain,
+                            const float* bias, void* dst, long long dst_stride, int dst_dtype,
+                            const int* dst_rows, long long dst_row_limit, int n_rows, int E, float eps,
+                            int form, int add, int* err, cudaStream_t stream) {
+  if (n_rows <= 0) return SGLC_OK;
+  if (E <= 0 || (form != NORM_LAYER && form != NORM_RMS)) return SGLC_ERR_ARGUMENT;
+  if (add && dst_dtype != SGLC_F32) return SGLC_ERR_ARGUMENT;
+  const size_t smem = (size_t)E * sizeof(float);
+  if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
+  const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : (E >= 128 ? 128 : (E >= 64 ? 64 : 32)));
+#define LAUNCH(TI, TO, ADD)                                                                          \
+  do {                                                                                               \
+    if (smem > 48 * 1024)                                                                            \
+      cudaFuncSetAttribute(norm_rows_kernel<TI, TO, ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           (int)smem);                                                               \
+    return sglc_launch(norm_rows_kernel<TI, TO, ADD>, dim3(n_rows), dim3(threads), smem, stream, 1,   \
+                       true, (const TI*)src, src_stride, src_rows, gain, bias, (TO*)dst, dst_stride, dst_rows,  \
+                       n_rows, E, eps, form, dst_row_limit, err);                                     \
+  } while (0)
+  if (src_dtype == SGLC_F32) {
+    if (add) LAUNCH(float, float, true);
+    if (dst_dtype == SGLC_F32) LAUNCH(float, float, false);
+    if (dst_dtype == SGLC_BF16) LAUNCH(float, __nv_bfloat16, false);
+  } else if (src_dtype == SGLC_BF16) {
+    if (add) LAUNCH(__nv_bfloat16, float, true);
+    if (dst_dtype == SGLC_F32) LAUNCH(__nv_bfloat16, float, false);
+    if (dst_dtype == SGLC_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, false);
+  }
+#undef LAUNCH
+  return SGLC_ERR_ARGUMENT;
+}

@@ -115,15 +115,28 @@ def _i32(t, what):
 
 
 # ---------------------------------------------------------------------------
-def embed(tokens, table, out, positions=None, pos_table=None, err_flag=None):
-    """out[t,:] = table[tokens[t],:] (+ pos_table[positions[t],:]); out is float32 [T,E]."""
-    _need_cuda(tokens, table, out, positions, pos_table)
+def embed(tokens, table, out, positions=None, pos_table=None, err_flag=None, inv_freq=None):
+    """out[t,:] = table[tokens[t],:] (+ pos_table[positions[t],:]); out is float32 [T,E].
+    With inv_freq (float64 [ceil(E/2)]) instead of a position table, the sinusoidal vector
+    sin/cos(positions[t] * inv_freq[i]) at entries 2i / 2i+1 is added."""
+    _need_cuda(tokens, table, out, positions, pos_table, inv_freq)
     _i32(tokens, "tokens")
     T, E = out.shape
     if out.dtype != torch.float32 or not out.is_contiguous():
         raise KernelError("embed: out must be contiguous float32")
     if table.shape[1] != E or not table.is_contiguous():
         raise KernelError(f"embed: table {tuple(table.shape)} does not match width {E}")
+    if inv_freq is not None:
+        _i32(positions, "positions")
+        if pos_table is not None or inv_freq.dtype != torch.float64 or inv_freq.numel() != (E + 1) // 2 \
+                or not inv_freq.is_contiguous():
+            raise KernelError("embed: inverse wavelengths must be float64, one per pair of columns, and come "
+                              "without a position table")
+        lib = build.load("embed")
+        code = lib.sglc_embed_sinusoid(_ptr(tokens), _ptr(positions), _ptr(table), _ptr(inv_freq), _ptr(out),
+                                       T, E, table.shape[0], _dt(table, "embed table"), _ptr(err_flag), _stream())
+        _check(lib, code, "embed_sinusoid")
+        return
     P = 0
     if pos_table is not None:
         _i32(positions, "positions")
@@ -213,11 +226,13 @@ def kv_write(k_src, v_src, cache, slots, n_kv_heads, head_dim):
 
 
 def attention_simt(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
-                   max_keys, max_q_len=None):
+                   max_keys, max_q_len=None, kv_shared=False):
     """Causal attention of T tokens over the paged cache, 32-bit arithmetic.
     q: [T, n_heads*head_dim] view; out likewise; block_table int32 [R, max_blocks].
     max_q_len: the longest portion among the tokens (1 when every request brings one token;
-    unknown: None); it only decides how many tokens share a block."""
+    unknown: None); it only decides how many tokens share a block.
+    kv_shared: cache is [n_pages, 1, n_kv_heads, page_size, head_dim], rows that are keys and
+    values at once."""
     _need_cuda(q, cache, block_table, token_req, positions, out)
     for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
         _i32(t, nm)
@@ -227,13 +242,16 @@ def attention_simt(q, cache, block_table, token_req, positions, out, n_heads, sc
         raise KernelError("attention: query/output rows do not match heads x head_dim")
     if q.dtype != cache.dtype:
         raise KernelError("attention: queries and cache must have one dtype")
+    if two != (1 if kv_shared else 2):
+        raise KernelError(f"attention: cache {tuple(cache.shape)} does not fit kv_shared={kv_shared}")
     lib = build.load("attention_simt")
-    code = lib.sglc_attention_simt(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
-                                   block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
-                                   out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
-                                   int(window or 0), int(max_keys), _dt(q, "attention q"),
-                                   _dt(cache, "cache"), n_pages, _ptr(tc_error_flag(q.device)),
-                                   int(max_q_len) if max_q_len else 2, _stream())
+    fn = lib.sglc_attention_simt_shared if kv_shared else lib.sglc_attention_simt
+    code = fn(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+              block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
+              out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
+              int(window or 0), int(max_keys), _dt(q, "attention q"),
+              _dt(cache, "cache"), n_pages, _ptr(tc_error_flag(q.device)),
+              int(max_q_len) if max_q_len else 2, _stream())
     _check(lib, code, f"attention_simt (head_dim {D}, up to {max_keys} keys)")
 
 
@@ -524,6 +542,111 @@ def sample(logits, params, hist_tok, hist_cnt, out_tok, out_logprob=None):
     code = lib.sglc_sample(_ptr(logits), logits.stride(0), V, n, _ptr(params), _ptr(hist_tok),
                            _ptr(hist_cnt), _ptr(out_tok), _ptr(out_logprob), _stream())
     _check(lib, code, "sample")
+
+
+# ---------------------------------------------------------------------------
+NORM_FORMS = {"layer": 0, "rms": 1}
+
+
+def norm_rows(src, gain, bias, eps, dst, form="layer", add=False, dst_rows=None, src_rows=None):
+    """dst[r,:] = norm(src[r,:]) * gain + bias (gain, bias: float32 vectors or None), `form`
+    "layer" (mean removed) or "rms"; src float32 or bfloat16 [n,E] with a free row stride.
+    add=True: dst (float32) += the normalised rows.  dst_rows (int32 [n]): row r goes to
+    dst[dst_rows[r], :] (dst [rows, E]: the rows of a paged cache seen flat).  src_rows (int32):
+    output row r is made from src[src_rows[r], :]; as many rows as dst has (or dst_rows names)."""
+    _need_cuda(src, gain, bias, dst, dst_rows, src_rows)
+    n, E = src.shape
+    if src_rows is not None:
+        _i32(src_rows, "src_rows")
+        n = dst.shape[0] if dst_rows is None else dst_rows.numel()
+        if src_rows.numel() < n:
+            raise KernelError("norm_rows: fewer source row indices than output rows")
+    if src.stride(1) != 1 or dst.stride(-1) != 1 or dst.shape[-1] != E or dst.dim() != 2:
+        raise KernelError("norm_rows: rows must be contiguous and of one width")
+    for v, nm in ((gain, "gain"), (bias, "bias")):
+        if v is not None and (v.dtype != torch.float32 or v.numel() != E or not v.is_contiguous()):
+            raise KernelError(f"norm_rows: {nm} must be a float32 vector of the row width")
+    if dst_rows is not None:
+        _i32(dst_rows, "dst_rows")
+        if dst_rows.numel() < n:
+            raise KernelError("norm_rows: fewer destination rows than source rows")
+    elif dst.shape[0] < n:
+        raise KernelError("norm_rows: fewer destination rows than source rows")
+    if add and dst.dtype != torch.float32:
+        raise KernelError("norm_rows: the sum goes into a float32 destination")
+    lib = build.load("norm_rows")
+    code = lib.sglc_norm_rows(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "norm source"), _ptr(src_rows),
+                              _ptr(gain),
+                              _ptr(bias), _ptr(dst), ctypes.c_longlong(dst.stride(0)), _dt(dst, "norm destination"),
+                              _ptr(dst_rows), ctypes.c_longlong(dst.shape[0]), n, E, ctypes.c_float(eps),
+                              NORM_FORMS[form], 1 if add else 0, _ptr(tc_error_flag(src.device)), _stream())
+    _check(lib, code, f"norm_rows (width {E})")
+
+
+GATED_SCAN_CHUNK = 128      # tokens per chunk of the gated scans' chunked way (gated_scan.cu: SCAN_CHUNK)
+
+
+def mingru_scan_workspace(n_requests, width, n_tokens, max_q_len):
+    """Floats of workspace mingru_scan needs for such a step: none while the longest portion fits
+    one chunk, else two per channel and chunk row plus one per channel and request."""
+    if max_q_len <= GATED_SCAN_CHUNK:
+        return 0
+    return int(width) * (2 * (int(n_tokens) // GATED_SCAN_CHUNK + int(n_requests)) + int(n_requests))
+
+
+def mingru_scan(gate, cand, out_gate, y, state, q_start, state_slots, n_requests, max_q_len, workspace=None):
+    """The minGRU recurrence over the step's tokens (see gated_scan.cu).  gate, cand, out_gate:
+    float32 [T,W] column ranges of one buffer; y: [T,W] float32 or bfloat16; state: float32
+    [n_slots, W], read and written in place for the requests' slots."""
+    _need_cuda(gate, cand, out_gate, y, state, q_start, state_slots, workspace)
+    T, W = gate.shape
+    for t in (gate, cand, out_gate):
+        if t.dtype != torch.float32 or tuple(t.shape) != (T, W) or t.stride(1) != 1 or t.stride(0) != gate.stride(0):
+            raise KernelError("mingru_scan: gate, candidate and output gate must be float32 [T,W] of one row stride")
+    if tuple(y.shape) != (T, W) or y.stride(1) != 1:
+        raise KernelError("mingru_scan: y must be [T,W]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != W or not state.is_contiguous():
+        raise KernelError("mingru_scan: the state is float32 [n_slots, W]")
+    _i32(q_start, "q_start")
+    _i32(state_slots, "state_slots")
+    need = mingru_scan_workspace(n_requests, W, T, max_q_len)
+    if need and (workspace is None or workspace.dtype != torch.float32 or workspace.numel() < need):
+        raise KernelError(f"mingru_scan: a step with portions of {max_q_len} tokens needs {need} floats of workspace")
+    lib = build.load("gated_scan")
+    if lib.sglc_gated_scan_chunk() != GATED_SCAN_CHUNK:
+        raise KernelError("gated_scan: the library's chunk size differs from the binding's")
+    code = lib.sglc_mingru_scan(_ptr(gate), _ptr(cand), _ptr(out_gate), ctypes.c_longlong(gate.stride(0)), _ptr(y),
+                                ctypes.c_longlong(y.stride(0)), _dt(y, "scan output"), _ptr(state), state.shape[0],
+                                _ptr(q_start), _ptr(state_slots), int(n_requests), W, T, int(max_q_len),
+                                _ptr(workspace), _ptr(tc_error_flag(gate.device)), _stream())
+    _check(lib, code, f"mingru_scan (width {W})", n_kernels=2 if need else 1)
+
+
+def depth_mix(x, hist, n_terms, weights):
+    """hist[n_terms-1] = x; x = sum_j weights[j] * hist[j], j < n_terms (32-bit).  x: float32
+    [T,E] contiguous; hist: float32 [>= n_terms, T, E] contiguous.  n_terms = 1: only the copy."""
+    _need_cuda(x, hist, weights)
+    if x.dtype != torch.float32 or hist.dtype != torch.float32 or not x.is_contiguous() or not hist.is_contiguous() \
+            or hist.shape[0] < n_terms or tuple(hist.shape[1:]) != tuple(x.shape):
+        raise KernelError("depth_mix: x float32 [T,E], hist float32 [n,T,E] with n >= n_terms")
+    if n_terms > 1 and (weights is None or weights.dtype != torch.float32 or weights.numel() < n_terms):
+        raise KernelError("depth_mix: one float32 weight per term")
+    lib = build.load("elementwise")
+    code = lib.sglc_depth_mix(_ptr(x), _ptr(hist), ctypes.c_longlong(x.numel()), int(n_terms), _ptr(weights), _stream())
+    _check(lib, code, "depth_mix")
+
+
+def xielu(src, dst, ap, an):
+    """dst = xIELU(src): ap*x^2 + x/2 for x > 0, an*(exp(x)-1-x) + x/2 otherwise."""
+    _need_cuda(src, dst)
+    rows, cols = src.shape
+    if tuple(dst.shape) != (rows, cols) or src.stride(1) != 1 or dst.stride(1) != 1:
+        raise KernelError("xielu: source and destination must be [rows, cols]")
+    lib = build.load("elementwise")
+    code = lib.sglc_xielu(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "xielu source"), _ptr(dst),
+                          ctypes.c_longlong(dst.stride(0)), _dt(dst, "xielu destination"), rows, cols,
+                          ctypes.c_float(ap), ctypes.c_float(an), _stream())
+    _check(lib, code, "xielu")
 
 
 def set_pdl(on):

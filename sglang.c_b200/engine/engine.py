@@ -49,7 +49,8 @@ class Engine:
         needs, cache_of = self.model.cache_needs()
         self.cache = CacheManager(needs, cache_of, self.page_size, n_pages, self.max_requests,
                                   make_tensor=runtime.make_tensor, cache_dtype=runtime.cache_dtype_name)
-        self.b_cap = (plan.max_positions + self.page_size - 1) // self.page_size
+        # a block table never has more entries than the model has positions, nor than the pool has pages
+        self.b_cap = min((plan.max_positions + self.page_size - 1) // self.page_size, self.cache.n_pages)
         self._paged = self.cache.paged_groups()
         self._any_window = any(self.cache.groups[gi].need.window is not None for gi in self._paged)
         self._rep = None                  # what a repeated step of single tokens updates in place

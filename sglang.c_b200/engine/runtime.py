@@ -101,3 +101,10 @@ class Runtime:
             return
         ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
                            scale, window, ctx.max_keys, max_q_len=ctx.max_q_len)
+
+    def attend_shared(self, ctx, q, binding, grp, out, n_heads, head_dim, scale, window):
+        """Causal attention of the step's queries over a cache whose rows are keys and values at
+        once (one shared head: a latent).  The rows of the step's own tokens are in the cache
+        already (whoever owns it wrote them)."""
+        ops.attention_simt(q, binding.tensor, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
+                           scale, window, ctx.max_keys, max_q_len=ctx.max_q_len, kv_shared=True)

@@ -114,6 +114,7 @@ class StepContext:
         self.groups: List[GroupStep] = []
         self.err_flag = None
         self.few_token_ok = False      # every matrix of the model's layers is small (see Runtime.gemm)
+        self.shared = {}               # what parts of different layers hand one another within the step
 
     def group(self, i):
         return self.groups[i]

@@ -1,7 +1,10 @@
 """Attention mixers."""
+import torch
+
 from ..cache.needs import CacheNeed
 from .base import Part
 from .linear import Linear, declare_linear
+from .plan import WeightDecl
 from .position import PositionEncoding
 from .registry import register_part
 
@@ -55,7 +58,7 @@ class CausalAttention(Part):
             return ((ctx.max_keys + g - 1) // g) * g
         return None
 
-    def forward(self, ctx, h, residual, cache, position=None):
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
         p = self.params
         H, Hkv, D = p["n_heads"], p["n_kv_heads"], p["head_dim"]
         T = h.shape[0]
@@ -77,5 +80,105 @@ class CausalAttention(Part):
         o = ctx.alloc((T, H * D), self.rt.act_dtype)
         ctx.rt.attend(ctx, q, k, v, cache, grp, o, H, Hkv, D, float(p["scale"]), p.get("window"),
                       kv_written=kv_written)
-        self.out.forward(ctx, o, residual=residual)
-        return residual
+        return self.out.forward(ctx, o, out=out, residual=residual)
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Part):
+    """Causal multi-head attention whose keys and values are made from one cached latent:
+    c = rms_norm(h·Wdkvᵀ) (kv_rank wide, the only thing kept per position);
+    head i: k = Wuk_i c, v = Wuv_i c, score = (q_i · k) * scale, ordinary softmax over the
+    positions up to the query's own; out = Wo · [heads' results side by side].
+    Queries are h·Wqᵀ, or, with `q_rank`, go through a latent of their own:
+    q = Wuq · rms_norm(h·Wdqᵀ).  No position enters.  With `own_latent` false the layer has no
+    Wdkv: it reads the latents another call cached (the plan's `cache_of`) through its own Wuk, Wuv.
+
+    Computed in the absorbed form: q_i · (Wuk_i c) = (Wuk_iᵀ q_i) · c and
+    sum_j p_j Wuv_i c_j = Wuv_i (sum_j p_j c_j), so attention runs on the latent itself as one
+    shared key/value head of size kv_rank, and Wuk_iᵀ is folded into the query projection, Wuv_i
+    into the output projection, once at load (in 64-bit, then rounded to the runtime's matrix
+    precision).  params: size, n_heads, qk_dim, v_dim, kv_rank, q_rank (None or a size), scale,
+    eps (of the latents' norms), own_latent, window."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, D, V, R = params["size"], params["n_heads"], params["qk_dim"], params["v_dim"], params["kv_rank"]
+        d = {"k_up": WeightDecl((H * D, R), "matrix"), "v_up": WeightDecl((H * V, R), "matrix"),
+             "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+        if params.get("q_rank"):
+            Q = params["q_rank"]
+            d.update({"q_down": WeightDecl((Q, E), "matrix"), "q_norm": WeightDecl((Q,), "norm_gain"),
+                      "q_up": WeightDecl((H * D, Q), "matrix")})
+        else:
+            d["q_weight"] = WeightDecl((H * D, E), "matrix")
+        if params.get("own_latent", True):
+            d.update({"kv_down": WeightDecl((R, E), "matrix"), "kv_norm": WeightDecl((R,), "norm_gain")})
+        return d
+
+    def load(self, tensors, store):
+        p = self.params
+        H, D, V, R, Q = p["n_heads"], p["qk_dim"], p["v_dim"], p["kv_rank"], p.get("q_rank")
+        k_up, v_up, w_o = tensors["k_up"], tensors["v_up"], tensors["out_weight"]
+        q_src = tensors["q_up"] if Q else tensors["q_weight"]
+
+        def fold_queries():       # [H*R, in]: head i's rows are Wuk_iᵀ · (head i's rows of the query projection)
+            uk = k_up.tensor.double().view(H, D, R)
+            wq = q_src.tensor.double().view(H, D, -1)
+            return torch.einsum("hdr,hdi->hri", uk, wq).reshape(H * R, -1)
+
+        def fold_output():        # [E, H*R]: head i's columns are (head i's columns of Wo) · Wuv_i
+            uv = v_up.tensor.double().view(H, V, R)
+            wo = w_o.tensor.double().view(-1, H, V)
+            return torch.einsum("ehv,hvr->ehr", wo, uv).reshape(-1, H * R)
+
+        self.q_abs = Linear(store.computed(f"fold({k_up.name},{q_src.name})", fold_queries), None)
+        self.out = Linear(store.computed(f"fold({w_o.name},{v_up.name})", fold_output), None)
+        self.q_norm = self.kv_norm = None
+        downs = []
+        if Q:
+            downs.append(tensors["q_down"])
+            self.q_norm = store.vector(tensors["q_norm"])
+        if p.get("own_latent", True):
+            downs.append(tensors["kv_down"])
+            self.kv_norm = store.vector(tensors["kv_norm"])
+        # the projections whose results go through a norm are one product with a 32-bit result
+        self.down = None
+        if downs:
+            self.down = Linear(store.computed("+".join(r.name for r in downs),
+                                              lambda: torch.cat([r.tensor.float() for r in downs], 0)), None)
+
+    def cache_need(self):
+        p = self.params
+        return CacheNeed.paged_kv(1, p["kv_rank"], p.get("window"), shared=True)
+
+    def workspace_per_token(self):
+        p = self.params
+        act = 4 if self.rt.dtype == "float32" else 2
+        return act * (2 * p["n_heads"] * p["kv_rank"] + (p.get("q_rank") or 0)) + 4 * ((p.get("q_rank") or 0) + p["kv_rank"])
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        from ..csrc import ops
+        p = self.params
+        H, R, Q = p["n_heads"], p["kv_rank"], p.get("q_rank") or 0
+        own = p.get("own_latent", True)
+        if own != cache.write:
+            raise ValueError("latent attention: a layer with its own latent projection owns its cache, one without reads another's")
+        T = h.shape[0]
+        eps = float(p["eps"])
+        grp = ctx.group(cache.group)
+        q_in = h
+        if self.down is not None:
+            low = ctx.alloc((T, self.down.out_size), torch.float32)
+            self.down.forward(ctx, h, out=low)
+            if Q:
+                q_in = ctx.alloc((T, Q), self.rt.act_dtype)
+                ops.norm_rows(ctx.columns(low, 0, Q), self.q_norm, None, eps, q_in, form="rms")
+            if own:
+                # the normalised latent goes straight into its cache rows (page * page_size + offset)
+                rows = cache.tensor.view(-1, R)
+                ops.norm_rows(ctx.columns(low, Q, Q + R), self.kv_norm, None, eps, rows, form="rms", dst_rows=grp.slots)
+        q = ctx.alloc((T, H * R), self.rt.act_dtype)
+        self.q_abs.forward(ctx, q_in, out=q)
+        o = ctx.alloc((T, H * R), self.rt.act_dtype)
+        ctx.rt.attend_shared(ctx, q, cache, grp, o, H, R, float(p["scale"]), p.get("window"))
+        return self.out.forward(ctx, o, out=out, residual=residual)

@@ -12,11 +12,16 @@ Interfaces by category (ctx is an `engine.step.StepContext`):
                 apply_embedding(ctx, x)          in-place change of x after the gather
                 rotate(ctx, q, k)                in-place change of queries/keys in a mixer
   norm          forward(ctx, x, out, rows=None)  out = norm(x[rows]) ; x float32 residual
+                add_into(ctx, y, residual)       residual += norm(y) (a norm behind a sublayer)
   mixer         cache_need() -> CacheNeed|None   what it keeps per request
-                forward(ctx, h, residual, cache, position)
+                forward(ctx, h, residual, cache, position, out=None)
                                                  residual += mix(h) using `cache`
-                                                 (a cache.CacheBinding, or None)
-  feed_forward  forward(ctx, h, residual)        residual += ff(h)
+                                                 (a cache.CacheBinding, or None); with `out`
+                                                 (float32 [T,E]) instead: out = mix(h)
+  feed_forward  forward(ctx, h, residual, out=None)
+                                                 residual += ff(h), or out = ff(h)
+  stream_mix    begin(ctx, x) / finish(ctx, x)   around a layer: x becomes a mix of this and
+                                                 earlier layers' results (kept in ctx.shared)
   block         forward(ctx, x, layer, cache, position)
                                                  runs norm1/mixer/norm2/ffn of `layer` on x
   head          forward(ctx, h, out)             out[W,V] float32 logits of h[W,E]

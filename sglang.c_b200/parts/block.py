@@ -1,4 +1,6 @@
 """Arrangements of norm, mixer and feed-forward around the residual stream."""
+import torch
+
 from .base import Part
 from .registry import register_part
 
@@ -25,4 +27,45 @@ class PreNormBlock(Part):
         layer.norm2.forward(ctx, x, h)
         layer.ffn.forward(ctx, h, residual=x)
         ctx.release(mark)
+        return x
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Part):
+    """A norm ahead of and a norm behind each sublayer:
+    x += norm1b(mixer(norm1(x))); x += norm2b(ffn(norm2(x))).  The second sublayer is there
+    only if the layer has an `ffn`.  A sublayer's result is a 32-bit buffer; the norm behind it
+    sums it into the 32-bit stream in the same kernel.  A layer with a `depth_mix` sub-part
+    (category stream_mix) hands x to it before and after."""
+
+    def workspace_per_token(self, layer):
+        act = 4 if self.rt.dtype == "float32" else 2
+        E = layer.norm1.params["size"]
+        inner = layer.mixer.workspace_per_token()
+        if "ffn" in layer.parts:
+            inner = max(inner, layer.ffn.workspace_per_token())
+        extra = layer.depth_mix.workspace_per_token() if "depth_mix" in layer.parts else 0
+        return (act + 4) * E + inner + extra
+
+    def forward(self, ctx, x, layer, cache, position=None):
+        T, E = x.shape
+        mix = layer.parts.get("depth_mix")
+        if mix is not None:
+            mix.begin(ctx, x)                # what it keeps for the step lies below the layers' buffers
+        mark = ctx.mark()
+        h = ctx.alloc((T, E), self.rt.act_dtype)
+        y = ctx.alloc((T, E), torch.float32)
+        layer.norm1.forward(ctx, x, h)
+        inner = ctx.mark()
+        layer.mixer.forward(ctx, h, residual=None, cache=cache, position=position, out=y)
+        ctx.release(inner)
+        layer.norm1b.add_into(ctx, y, x)
+        if "ffn" in layer.parts:
+            layer.norm2.forward(ctx, x, h)
+            layer.ffn.forward(ctx, h, residual=None, out=y)
+            ctx.release(inner)
+            layer.norm2b.add_into(ctx, y, x)
+        ctx.release(mark)
+        if mix is not None:
+            mix.finish(ctx, x)
         return x

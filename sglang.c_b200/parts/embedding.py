@@ -21,7 +21,12 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx, out, position=None):
         ptab = position.additive_table() if position is not None else None
-        if ptab is not None and ptab.dtype == self.table.dtype:
+        waves = getattr(position, "inverse_wavelengths", None)
+        if waves is not None:
+            # a position vector computed from the position itself goes in with the gather
+            ops.embed(ctx.tokens, self.table, out, positions=ctx.positions, inv_freq=waves(),
+                      err_flag=ctx.err_flag)
+        elif ptab is not None and ptab.dtype == self.table.dtype:
             ops.embed(ctx.tokens, self.table, out, positions=ctx.positions, pos_table=ptab,
                       err_flag=ctx.err_flag)
         else:

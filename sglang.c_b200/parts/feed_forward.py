@@ -1,6 +1,9 @@
 """Feed-forward parts."""
+import torch
+
 from .base import Part
 from .linear import Linear, declare_linear
+from .plan import WeightDecl
 from .registry import register_part
 
 
@@ -8,8 +11,10 @@ from .registry import register_part
 class MLP(Part):
     """residual += act(h·W_up + b_up)·W_down + b_down
     (reference src/gpt2.c:283-292; activation src/ops.c:233-241).
-    params: size, inner_size, activation ("gelu_tanh" | "gelu_erf"), bias,
-    weight_layout ("conv1d" = [in,out] in the file, "linear" = [out,in])."""
+    params: size, inner_size, activation ("gelu_tanh" | "gelu_erf" | "xielu"), bias,
+    weight_layout ("conv1d" = [in,out] in the file, "linear" = [out,in]).
+    "xielu" carries two numbers (p, q) of its own in a tensor `act_params`:
+    act(z) = softplus(p) z^2 + z/2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2 otherwise."""
 
     @classmethod
     def declare_weights(cls, params):
@@ -18,19 +23,37 @@ class MLP(Part):
         down = declare_linear(params["inner_size"], params["size"], lay, bias, init="residual_matrix")
         d = {"up_" + k: v for k, v in up.items()}
         d.update({"down_" + k: v for k, v in down.items()})
+        if params["activation"] == "xielu":
+            d["act_params"] = WeightDecl((2,), "bias")
         return d
 
     def load(self, tensors, store):
         lay = self.params.get("weight_layout", "linear")
         self.up = Linear.from_refs(store, tensors["up_weight"], tensors.get("up_bias"), lay)
         self.down = Linear.from_refs(store, tensors["down_weight"], tensors.get("down_bias"), lay)
+        self.act_params = None
+        if self.params["activation"] == "xielu":
+            pq = tensors["act_params"].tensor.double()
+            sp = torch.nn.functional.softplus(pq)
+            self.act_params = (float(sp[0]), 0.5 + float(sp[1]))
 
     def workspace_per_token(self):
-        return (4 if self.rt.dtype == "float32" else 2) * self.params["inner_size"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        return (act + (4 if self.act_in_own_kernel() else 0)) * self.params["inner_size"]
 
-    def forward(self, ctx, h, residual):
+    def act_in_own_kernel(self):
+        """An activation with numbers of its own has no epilogue in the products: the product's
+        32-bit result goes through a kernel of the activation."""
+        return self.params["activation"] == "xielu"
+
+    def forward(self, ctx, h, residual, out=None):
+        from ..csrc import ops
         T = h.shape[0]
         u = ctx.alloc((T, self.params["inner_size"]), self.rt.act_dtype)
-        self.up.forward(ctx, h, out=u, act=self.params["activation"])
-        self.down.forward(ctx, u, residual=residual)
-        return residual
+        if self.act_in_own_kernel():
+            z = ctx.alloc((T, self.params["inner_size"]), torch.float32)
+            self.up.forward(ctx, h, out=z)
+            ops.xielu(z, u, *self.act_params)
+        else:
+            self.up.forward(ctx, h, out=u, act=self.params["activation"])
+        return self.down.forward(ctx, u, out=out, residual=residual)

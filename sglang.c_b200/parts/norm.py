@@ -9,17 +9,50 @@ from .registry import register_part
 class LayerNorm(Part):
     """y = (x-mean)/sqrt(var+eps)*weight + bias over the last axis, biased
     variance, statistics in 32-bit (reference src/ops.c:199-218).
-    params: size, eps."""
+    params: size, eps, bias (default true; false: a gain only)."""
+
+    form = "layer"
 
     @classmethod
     def declare_weights(cls, params):
-        return {"weight": WeightDecl((params["size"],), "norm_gain"),
-                "bias": WeightDecl((params["size"],), "norm_bias")}
+        d = {"weight": WeightDecl((params["size"],), "norm_gain")}
+        if params.get("bias", True):
+            d["bias"] = WeightDecl((params["size"],), "norm_bias")
+        return d
 
     def load(self, tensors, store):
         self.weight = store.vector(tensors["weight"])
-        self.bias = store.vector(tensors["bias"])
+        self.bias = store.vector(tensors["bias"]) if "bias" in tensors else None
 
     def forward(self, ctx, x, out, rows=None):
-        ops.layernorm(x, self.weight, self.bias, float(self.params["eps"]), out, rows=rows)
+        if self.bias is not None and self.form == "layer":
+            ops.layernorm(x, self.weight, self.bias, float(self.params["eps"]), out, rows=rows)
+        else:
+            src = x[:out.shape[0]] if rows is None else x
+            ops.norm_rows(src, self.weight, self.bias, float(self.params["eps"]), out, form=self.form,
+                          src_rows=rows)
         return out
+
+    def add_into(self, ctx, y, residual):
+        """residual += norm(y): the norm behind a sublayer, summed into the 32-bit stream."""
+        ops.norm_rows(y, self.weight, self.bias, float(self.params["eps"]), residual[:y.shape[0]],
+                      form=self.form, add=True)
+        return residual
+
+    def scatter(self, ctx, y, dst, dst_rows):
+        """dst[dst_rows[r], :] = norm(y[r, :]): normalised rows straight into a cache's rows."""
+        ops.norm_rows(y, self.weight, self.bias, float(self.params["eps"]), dst, form=self.form,
+                      dst_rows=dst_rows)
+        return dst
+
+
+@register_part("norm", "rms_norm")
+class RMSNorm(LayerNorm):
+    """y = x / sqrt(mean(x^2) + eps) * weight, eps inside the root, statistics in 32-bit.
+    params: size, eps."""
+
+    form = "rms"
+
+    @classmethod
+    def declare_weights(cls, params):
+        return {"weight": WeightDecl((params["size"],), "norm_gain")}

@@ -39,3 +39,20 @@ class LearnedAbsolutePositions(PositionEncoding):
 
     def apply_embedding(self, ctx, x):
         ops.add_rows(x, ctx.positions, self.table)
+
+
+@register_part("position", "sinusoidal")
+class SinusoidalPositions(PositionEncoding):
+    """A fixed vector added at the embedding, computed from the position, no table and no
+    bound: entry 2i is sin(p * base^(-2i/size)), entry 2i+1 the cosine of the same angle.
+    The inverse wavelengths are made once, in 64-bit; the embedding kernel forms the angle.
+    params: size, base."""
+
+    def load(self, tensors, store):
+        import torch
+        size, base = int(self.params["size"]), float(self.params["base"])
+        i = torch.arange((size + 1) // 2, dtype=torch.float64)
+        self.inv_freq = (base ** (-2.0 * i / size)).contiguous().to(self.rt.device)
+
+    def inverse_wavelengths(self):
+        return self.inv_freq

@@ -2,7 +2,7 @@
 `kind`; building a model looks the class up here.  Anything registered from
 outside the package (a test's toy mixer, a new feed-forward) is used the same
 way as the built-in parts."""
-CATEGORIES = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head")
+CATEGORIES = ("embedding", "position", "norm", "mixer", "feed_forward", "block", "head", "stream_mix")
 _REGISTRY = {c: {} for c in CATEGORIES}
 
 
@@ -37,4 +37,4 @@ def registered(category):
 
 def _load_builtin():
     from . import (attention, block, embedding, feed_forward, head, norm,  # noqa: F401
-                   position)
+                   position, recurrent, stream_mix)

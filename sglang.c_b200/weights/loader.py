@@ -222,6 +222,16 @@ class DeviceStore:
             self.largest_layer_matrix = max(self.largest_layer_matrix, t.numel())
         return t
 
+    def computed(self, key, make, kind="matrix"):
+        """A tensor a part derives from the file's tensors at load (projections laid side by side,
+        or folded into one another): `make()` returns it on the host in float32 or float64; it
+        goes to the device as a matrix in the runtime's precision or as a float32 vector."""
+        dt = self.rt.matrix_dtype if kind == "matrix" else torch.float32
+        t = self._put((key, "computed", kind), lambda: make().to(dt).contiguous().to(self.rt.device))
+        if kind == "matrix" and self.in_layer:
+            self.largest_layer_matrix = max(self.largest_layer_matrix, t.numel())
+        return t
+
     def vector(self, ref):
         return self._put((ref.name, "vector"),
                          lambda: ref.tensor.to(torch.float32).contiguous().to(self.rt.device))
