@@ -81,7 +81,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         int use_cluster, float* __restrict__ ws, int* __restrict__ counters,
                         const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
                         int new_stride, const int* __restrict__ slots, int nb_max, int* __restrict__ err,
-                        const int* __restrict__ token_list, int n_pages) {
+                        const int* __restrict__ token_list, int n_pages, int kv_shared) {
   extern __shared__ float smem[];
   __shared__ float red[33];
   __shared__ int s_last;
@@ -151,9 +151,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   const int nk = k1 > k0 ? k1 - k0 : 0;
   const int G = H / Hkv;
   const int hk = h / G;
-  const size_t page_elems = (size_t)2 * Hkv * page_size * D;
+  // kv_shared: a page holds one block of rows that are keys and values at once (a latent)
+  const size_t page_elems = (size_t)(kv_shared ? 1 : 2) * Hkv * page_size * D;
   const size_t head_off = (size_t)hk * page_size * D;
-  const size_t v_off = (size_t)Hkv * page_size * D;
+  const size_t v_off = kv_shared ? 0 : (size_t)Hkv * page_size * D;
   const bool fused = k_new != nullptr;
   const __nv_bfloat16* kn = fused ? k_new + (size_t)t * new_stride + (size_t)hk * D : nullptr;
   const __nv_bfloat16* vn = fused ? v_new + (size_t)t * new_stride + (size_t)hk * D : nullptr;
@@ -476,15 +477,16 @@ SGLC_API int sglc_attention_decode_splits(int T, int H, int max_keys) {
 // T: the number of tokens this launch serves (all of the step's, or those named by token_list).
 // k_new, v_new (bfloat16 [T][new_stride]) and slots (int32 [T]) may be null; when given, the
 // tokens' own keys and values are read from them and written into the cache by this launch.
-SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
-                                   const int* block_table, int bt_stride, const int* token_req,
-                                   const int* positions, void* out, int o_stride, int T, int H,
-                                   int Hkv, int D, int page_size, float scale, int window,
-                                   int max_keys, int n_splits, float* ws, int* counters,
-                                   const void* k_new, const void* v_new, int new_stride,
-                                   const int* slots, int* err, const int* token_list, int n_pages,
-                                   cudaStream_t stream) {
+static int attention_decode_run(const void* q, int q_stride, void* cache,
+                                const int* block_table, int bt_stride, const int* token_req,
+                                const int* positions, void* out, int o_stride, int T, int H,
+                                int Hkv, int D, int page_size, float scale, int window,
+                                int max_keys, int n_splits, float* ws, int* counters,
+                                const void* k_new, const void* v_new, int new_stride,
+                                const int* slots, int* err, const int* token_list, int n_pages,
+                                int kv_shared, cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
+  if (kv_shared && k_new) return SGLC_ERR_ARGUMENT;     // shared rows are written by whoever makes them
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_splits < 1)
     return SGLC_ERR_ARGUMENT;
   if (D % 8 != 0 || D > 256 || H > 65535 || n_splits > 65535) return SGLC_ERR_UNSUPPORTED;
@@ -510,7 +512,34 @@ SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
                      (__nv_bfloat16*)cache, block_table, bt_stride, token_req, positions,
                      (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_splits,
                      chunk_cap, use_cluster, ws, counters, (const __nv_bfloat16*)k_new,
-                     (const __nv_bfloat16*)v_new, new_stride, slots, nb_max, err, token_list, n_pages);
+                     (const __nv_bfloat16*)v_new, new_stride, slots, nb_max, err, token_list, n_pages,
+                     kv_shared);
+}
+
+SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
+                                   const int* block_table, int bt_stride, const int* token_req,
+                                   const int* positions, void* out, int o_stride, int T, int H,
+                                   int Hkv, int D, int page_size, float scale, int window,
+                                   int max_keys, int n_splits, float* ws, int* counters,
+                                   const void* k_new, const void* v_new, int new_stride,
+                                   const int* slots, int* err, const int* token_list, int n_pages,
+                                   cudaStream_t stream) {
+  return attention_decode_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride, T,
+                              H, Hkv, D, page_size, scale, window, max_keys, n_splits, ws, counters, k_new, v_new,
+                              new_stride, slots, err, token_list, n_pages, 0, stream);
+}
+
+// The same over pages [n_pages][1][Hkv][page_size][D] whose rows are keys and values at once
+// (attention over a cached latent).  The rows of the step's own tokens are in the cache already.
+SGLC_API int sglc_attention_decode_shared(const void* q, int q_stride, void* cache,
+                                          const int* block_table, int bt_stride, const int* token_req,
+                                          const int* positions, void* out, int o_stride, int T, int H,
+                                          int Hkv, int D, int page_size, float scale, int window,
+                                          int max_keys, int n_splits, float* ws, int* counters, int* err,
+                                          const int* token_list, int n_pages, cudaStream_t stream) {
+  return attention_decode_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride, T,
+                              H, Hkv, D, page_size, scale, window, max_keys, n_splits, ws, counters, nullptr,
+                              nullptr, 0, nullptr, err, token_list, n_pages, 1, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -621,6 +650,6 @@ SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const vo
       /*k_new=*/(const __nv_bfloat16*)nullptr, /*v_new=*/(const __nv_bfloat16*)nullptr, 0,
       /*slots=*/(const int*)nullptr, nb_max,
       /*err=*/reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(base) + NOALLOC_STATUS_OFFSET),
-      /*token_list=*/(const int*)nullptr, /*n_pages=*/0x7fffffff);
+      /*token_list=*/(const int*)nullptr, /*n_pages=*/0x7fffffff, /*kv_shared=*/0);
   return sglc_launch_status();
 }

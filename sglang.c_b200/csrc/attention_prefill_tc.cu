@@ -61,6 +61,7 @@ struct Args {
   int skip_single;        // requests that bring one token are served by the decode kernel
   int split_min;          // key tiles from which a query tile is shared by the cluster's two blocks
   int* err;
+  int kv_shared;          // pages [1][Hkv][page_size][D]: one block of rows serves as keys and as values
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -241,7 +242,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             tma_load_5d(sK + s * TILE_BYTES + blk * (BKV * 128) + row_off, &map_kv, &ctl.kv_full[s],
                         blk * 64, 0, hk, 0, page);
             tma_load_5d(sV + s * TILE_BYTES + blk * (BKV * 128) + row_off, &map_kv, &ctl.kv_full[s],
-                        blk * 64, 0, hk, 1, page);
+                        blk * 64, 0, hk, a.kv_shared ? 0 : 1, page);
           }
         }
       }
@@ -262,9 +263,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       cp_async_commit();
     }
     const int* bt = a.block_table + (size_t)r * a.bt_stride;
-    const size_t page_elems = (size_t)2 * a.Hkv * a.page_size * D;
+    const size_t page_elems = (size_t)(a.kv_shared ? 1 : 2) * a.Hkv * a.page_size * D;
     const size_t head_off = (size_t)hk * a.page_size * D;
-    const size_t v_off = (size_t)a.Hkv * a.page_size * D;
+    const size_t v_off = a.kv_shared ? 0 : (size_t)a.Hkv * a.page_size * D;
     auto issue_tile = [&](int j) {
       const int s = j % KV_STAGES;
       const int key0 = (kt0 + j) * BKV;
@@ -582,7 +583,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 
 // ---- host: tensor maps, kept per (pointer, shape) ----
 struct KeyQ { const void* p; uint64_t rows, cols, ld; };
-struct KeyKV { const void* p; int D, ps, Hkv, n_pages; };
+struct KeyKV { const void* p; int D, ps, Hkv, n_pages, halves; };
 std::mutex g_mutex;
 std::vector<std::pair<KeyQ, CUtensorMap>> g_qmaps;
 std::vector<std::pair<KeyKV, CUtensorMap>> g_kvmaps;
@@ -602,21 +603,22 @@ bool get_q_map(CUtensorMap* out, const void* q, uint64_t rows, uint64_t cols, ui
   return true;
 }
 
-// One layer's pages [n_pages][2][Hkv][page_size][D] as a 5-D tensor, boxes of one page's rows of
-// one head, 64 elements (128 bytes) wide, in the 128-byte swizzle.
-bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int n_pages) {
+// One layer's pages [n_pages][halves][Hkv][page_size][D] (halves = 2: keys, values; 1: rows that
+// are both) as a 5-D tensor, boxes of one page's rows of one head, 64 elements (128 bytes) wide,
+// in the 128-byte swizzle.
+bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int n_pages, int halves) {
   std::lock_guard<std::mutex> lock(g_mutex);
   for (auto& e : g_kvmaps)
     if (e.first.p == cache && e.first.D == D && e.first.ps == ps && e.first.Hkv == Hkv &&
-        e.first.n_pages == n_pages) {
+        e.first.n_pages == n_pages && e.first.halves == halves) {
       *out = e.second;
       return true;
     }
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn || ((uintptr_t)cache & 15) || ps > 256) return false;
-  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, 2, (cuuint64_t)n_pages};
+  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, (cuuint64_t)halves, (cuuint64_t)n_pages};
   cuuint64_t strides[4] = {(cuuint64_t)D * 2, (cuuint64_t)ps * D * 2, (cuuint64_t)Hkv * ps * D * 2,
-                           (cuuint64_t)2 * Hkv * ps * D * 2};
+                           (cuuint64_t)halves * Hkv * ps * D * 2};
   cuuint32_t box[5] = {64, (cuuint32_t)ps, 1, 1, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUtensorMap m;
@@ -625,7 +627,7 @@ bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return false;
   if (g_kvmaps.size() > 1024) g_kvmaps.clear();
-  g_kvmaps.push_back({KeyKV{cache, D, ps, Hkv, n_pages}, m});
+  g_kvmaps.push_back({KeyKV{cache, D, ps, Hkv, n_pages, halves}, m});
   *out = m;
   return true;
 }
@@ -661,12 +663,12 @@ SGLC_API int sglc_attention_prefill_tc_supports(int D) { return D == 64 || D == 
 // cache: one layer's pages [n_pages][2][Hkv][page_size][D]; kv_len[r]: the request's length after
 // this step (its last query sits at kv_len-1); max_q_len: the longest portion (sizes the grid).
 // T: rows of q; n_pages: pages of the cache tensor.
-SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* cache,
-                                       const int* block_table, int bt_stride, const int* q_start,
-                                       const int* kv_len, void* out, int o_stride, int R,
-                                       int max_q_len, int H, int Hkv, int D, int page_size,
-                                       float scale, int window, int T, int n_pages, int skip_single,
-                                       int* err, cudaStream_t stream) {
+static int attention_prefill_run(const void* q, int q_stride, const void* cache,
+                                 const int* block_table, int bt_stride, const int* q_start,
+                                 const int* kv_len, void* out, int o_stride, int R,
+                                 int max_q_len, int H, int Hkv, int D, int page_size,
+                                 float scale, int window, int T, int n_pages, int skip_single,
+                                 int* err, int kv_shared, cudaStream_t stream) {
   if (R <= 0 || max_q_len <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0) return SGLC_ERR_ARGUMENT;
   if (!(D == 64 || D == 128) || H > 65535 || R > 32767 || max_q_len > 65535 * BQ || !(scale > 0.0f)) return SGLC_ERR_UNSUPPORTED;
@@ -685,6 +687,7 @@ SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* 
   a.err = err;
   a.skip_single = skip_single;
   a.split_min = g_split_min;
+  a.kv_shared = kv_shared;
   // TMA needs whole pages inside a 128-key tile and rows it can address
   CUtensorMap mq, mkv;
   memset(&mq, 0, sizeof(mq));
@@ -692,9 +695,33 @@ SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* 
   a.use_tma = 0;
   if (BKV % page_size == 0 && T > 0 && n_pages > 0) {
     bool ok = get_q_map(&mq, q, (uint64_t)T, (uint64_t)H * D, (uint64_t)q_stride) &&
-              get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages);
+              get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages, kv_shared ? 1 : 2);
     a.use_tma = ok ? 1 : 0;
   }
   if (D == 64) return launch<64>(mq, mkv, a, R, max_q_len, stream);
   return launch<128>(mq, mkv, a, R, max_q_len, stream);
+}
+
+SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* cache,
+                                       const int* block_table, int bt_stride, const int* q_start,
+                                       const int* kv_len, void* out, int o_stride, int R,
+                                       int max_q_len, int H, int Hkv, int D, int page_size,
+                                       float scale, int window, int T, int n_pages, int skip_single,
+                                       int* err, cudaStream_t stream) {
+  return attention_prefill_run(q, q_stride, cache, block_table, bt_stride, q_start, kv_len, out, o_stride, R,
+                               max_q_len, H, Hkv, D, page_size, scale, window, T, n_pages, skip_single, err, 0,
+                               stream);
+}
+
+// The same over pages [n_pages][1][Hkv][page_size][D] whose rows are keys and values at once
+// (attention over a cached latent): both operands of a tile are loaded from the same rows.
+SGLC_API int sglc_attention_prefill_tc_shared(const void* q, int q_stride, const void* cache,
+                                              const int* block_table, int bt_stride, const int* q_start,
+                                              const int* kv_len, void* out, int o_stride, int R,
+                                              int max_q_len, int H, int Hkv, int D, int page_size,
+                                              float scale, int window, int T, int n_pages, int skip_single,
+                                              int* err, cudaStream_t stream) {
+  return attention_prefill_run(q, q_stride, cache, block_table, bt_stride, q_start, kv_len, out, o_stride, R,
+                               max_q_len, H, Hkv, D, page_size, scale, window, T, n_pages, skip_single, err, 1,
+                               stream);
 }

@@ -10,8 +10,12 @@
 
 // element types a launcher takes, as small integers across the C interface
 enum { SGLC_F32 = 0, SGLC_BF16 = 1 };
-// epilogue activations
-enum { SGLC_ACT_NONE = 0, SGLC_ACT_GELU_TANH = 1, SGLC_ACT_GELU_ERF = 2 };
+// epilogue activations.  The low byte of an `act` argument is the kind; an activation with numbers
+// of its own (xIELU) carries, in the next byte, the slot of this library's parameter table that
+// holds them (sglc_set_act_params fills a slot, once, when a model is loaded).
+enum { SGLC_ACT_NONE = 0, SGLC_ACT_GELU_TANH = 1, SGLC_ACT_GELU_ERF = 2, SGLC_ACT_XIELU = 3 };
+#define SGLC_ACT_SLOTS 256
+__constant__ float2 c_sglc_act_params[SGLC_ACT_SLOTS];
 
 // codes a launcher returns besides cudaError_t values (those are > 0)
 enum { SGLC_OK = 0, SGLC_ERR_UNSUPPORTED = -2, SGLC_ERR_ARGUMENT = -3 };
@@ -78,6 +82,11 @@ __device__ __forceinline__ bool sglc_index_ok(long long, long long, int*) { retu
 
 #define SGLC_DEFINE_ERROR_STRING()                                            \
   SGLC_API void sglc_set_pdl(int on) { g_sglc_pdl = on; }                     \
+  SGLC_API int sglc_set_act_params(int slot, float a, float b) {              \
+    if (slot < 0 || slot >= SGLC_ACT_SLOTS) return SGLC_ERR_ARGUMENT;         \
+    const float2 v = make_float2(a, b);                                       \
+    return (int)cudaMemcpyToSymbol(c_sglc_act_params, &v, sizeof(v), (size_t)slot * sizeof(float2)); \
+  }                                                                           \
   SGLC_API const char* sglc_error_string(int code) {                          \
     if (code == SGLC_ERR_UNSUPPORTED) return "size not supported by this kernel"; \
     if (code == SGLC_ERR_ARGUMENT) return "bad argument";                     \
@@ -105,9 +114,18 @@ __device__ __forceinline__ float gelu_tanh_f32(float u) {
 __device__ __forceinline__ float gelu_erf_f32(float u) {
   return 0.5f * u * (1.0f + erff(u * 0.70710678118654752440f));
 }
+// xIELU with the two numbers ap > 0, an:  u > 0: ap u^2 + u/2;  u <= 0: an (exp(u) - 1 - u) + u/2
+__device__ __forceinline__ float xielu_f32(float u, float ap, float an) {
+  return u > 0.0f ? fmaf(ap * u, u, 0.5f * u) : fmaf(an, expm1f(u) - u, 0.5f * u);
+}
 __device__ __forceinline__ float apply_act(float u, int act) {
+  if (act == SGLC_ACT_NONE) return u;
   if (act == SGLC_ACT_GELU_TANH) return gelu_tanh_f32(u);
   if (act == SGLC_ACT_GELU_ERF) return gelu_erf_f32(u);
+  if ((act & 0xff) == SGLC_ACT_XIELU) {
+    const float2 p = c_sglc_act_params[(act >> 8) & 0xff];
+    return xielu_f32(u, p.x, p.y);
+  }
   return u;
 }
 
@@ -121,9 +139,21 @@ __device__ __forceinline__ float gelu_tanh_sigmoid(float u) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * 1.4426950408889634f));
   return __fdividef(u, 1.0f + e);
 }
+// (the exponential of the fast kind, as in the GELU above: the tensor-core products round the
+// result to bfloat16, and where exp(u) - 1 - u cancels, u/2 carries the value)
+__device__ __forceinline__ float xielu_fast(float u, float ap, float an) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(u * 1.4426950408889634f));
+  return u > 0.0f ? fmaf(ap * u, u, 0.5f * u) : fmaf(an, (e - 1.0f) - u, 0.5f * u);
+}
 __device__ __forceinline__ float act_tc(float u, int act) {
+  if (act == SGLC_ACT_NONE) return u;
   if (act == SGLC_ACT_GELU_TANH) return gelu_tanh_sigmoid(u);
   if (act == SGLC_ACT_GELU_ERF) return gelu_erf_f32(u);
+  if ((act & 0xff) == SGLC_ACT_XIELU) {
+    const float2 p = c_sglc_act_params[(act >> 8) & 0xff];
+    return xielu_fast(u, p.x, p.y);
+  }
   return u;
 }
 

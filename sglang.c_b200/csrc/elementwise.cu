@@ -65,10 +65,6 @@ SGLC_API int sglc_depth_mix(float* x, float* hist, long long n, int n_terms, con
   return sglc_launch(depth_mix_kernel<false>, dim3(blocks), dim3(256), 0, stream, 1, true, x, hist, n, n_terms, w);
 }
 
-__device__ __forceinline__ float xielu_f32(float v, float ap, float an) {
-  return v > 0.0f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
-}
-
 template <typename TI, typename TO>
 __global__ void xielu_kernel(const TI* __restrict__ src, long long src_stride, TO* __restrict__ dst,
                              long long dst_stride, int rows, int cols, float ap, float an) {

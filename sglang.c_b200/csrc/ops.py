@@ -9,7 +9,43 @@ import torch
 from . import build
 
 F32, BF16 = 0, 1
-ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2, "xielu": 3}
+ACT_SLOTS = 256              # parameter slots per kernel library (common.cuh: SGLC_ACT_SLOTS)
+_act_slots = []              # slot -> (a, b), as registered
+_act_synced = {}             # library name -> slots already written into it
+
+
+def _act(act):
+    """The integer a launcher takes: the kind, and for ("xielu", slot) the slot in the next byte."""
+    if isinstance(act, tuple):
+        return ACT[act[0]] | (int(act[1]) << 8)
+    if act == "xielu":
+        raise KernelError("xielu needs its parameters: pass (\"xielu\", slot) from register_act_params()")
+    return ACT[act]
+
+
+def register_act_params(a, b, libraries):
+    """Give the two numbers of an activation a slot in the parameter tables of the named kernel
+    libraries (equal numbers share a slot) and return it, or None when the tables are full (the
+    caller then applies the activation with a kernel of its own).  Done when a model is loaded,
+    never inside a step: the copy into a library's table synchronises."""
+    pair = (float(a), float(b))
+    if pair in _act_slots:
+        slot = _act_slots.index(pair)
+    elif len(_act_slots) < ACT_SLOTS:
+        _act_slots.append(pair)
+        slot = len(_act_slots) - 1
+    else:
+        return None
+    for name in libraries:
+        lib = build.load(name)
+        done = _act_synced.get((name, id(lib)), 0)
+        for i in range(done, len(_act_slots)):
+            code = lib.sglc_set_act_params(i, ctypes.c_float(_act_slots[i][0]), ctypes.c_float(_act_slots[i][1]))
+            if code != 0:
+                raise KernelError(f"{name}: setting activation parameters failed (code {code})")
+        _act_synced[(name, id(lib))] = len(_act_slots)
+    return slot
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 
@@ -201,7 +237,7 @@ def gemm_simt(a, w, bias, out=None, residual=None, act=None):
     lib = build.load("gemm_simt")
     code = lib.sglc_gemm_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
                               a.stride(0), dst.stride(0), _dt(a, "gemm input"),
-                              _dt(dst, "gemm output"), ACT[act], _stream())
+                              _dt(dst, "gemm output"), _act(act), _stream())
     _check(lib, code, f"gemm_simt M={M} N={N} K={K}")
 
 
@@ -327,7 +363,7 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None, supported=False):
     err = _tc_buffers(a.device)[2]
     code = lib.sglc_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
                             a.stride(0), dst.stride(0), 1 if dst.dtype == torch.float32 else 0,
-                            ACT[act], _ptr(err), _stream())
+                            _act(act), _ptr(err), _stream())
     _check(lib, code, f"gemm_tc M={M} N={N} K={K}")
 
 
@@ -363,7 +399,7 @@ def gemm_tc_form(M, N, K, act=None):
     """Which of gemm_tc's kernels a product of these sizes takes: "few" (up to 128 tokens: weights on
     the MMA's 128-row side, split-K over a cluster), "stream" (many tokens, one block a tile) or "pair"
     (many tokens on pairs of SMs)."""
-    return ("few", "stream", "pair")[build.load("gemm_tc").sglc_gemm_tc_form(int(M), int(N), int(K), ACT[act])]
+    return ("few", "stream", "pair")[build.load("gemm_tc").sglc_gemm_tc_form(int(M), int(N), int(K), _act(act))]
 
 
 FEW_MAX_TOKENS = 2           # products of so few tokens go to gemm_few ...
@@ -395,7 +431,7 @@ def gemm_few(a, w, bias, out=None, residual=None, act=None):
         raise KernelError("gemm_few: output must be float32 or bfloat16")
     code = lib.sglc_gemm_few(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
                              a.stride(0), dst.stride(0), 1 if dst.dtype == torch.float32 else 0,
-                             ACT[act], _stream())
+                             _act(act), _stream())
     _check(lib, code, f"gemm_few M={M} N={N} K={K}")
 
 
@@ -494,6 +530,44 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
     _check(lib, code, f"attention_decode (head_dim {D}, up to {max_keys} keys)")
 
 
+def attention_decode_shared(q, cache, block_table, token_req, positions, out, n_heads, scale, window, max_keys,
+                            token_list=None, n_tokens=None):
+    """Attention of single decoded tokens over a bfloat16 cache [n_pages, 1, n_kv_heads, page_size,
+    head_dim] whose rows are keys and values at once (a latent), keys split across blocks and
+    merged in a fixed order; the rows of the step's own tokens are in the cache already.
+    token_req None: token t belongs to the step's t-th request.  token_list (int32, its first
+    n_tokens entries; needs token_req): the tokens to serve."""
+    _need_cuda(q, cache, block_table, token_req, positions, out, token_list)
+    for t, nm in ((block_table, "block_table"), (positions, "positions")):
+        _i32(t, nm)
+    T = q.shape[0]
+    if token_req is not None:
+        _i32(token_req, "token_req")
+    if token_list is not None:
+        _i32(token_list, "token_list")
+        if token_req is None:
+            raise KernelError("attention_decode_shared: a list of some tokens needs token_req")
+        T = int(n_tokens)
+    n_pages, one, Hkv, page_size, D = cache.shape
+    if one != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_shared: bfloat16 queries, output and cache [n_pages,1,heads,page,dim]")
+    if q.shape[1] != n_heads * D or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention_decode_shared: query/output rows do not match heads x head_dim")
+    lib = build.load("attention_decode")
+    ws, counters, err = _tc_buffers(q.device)
+    splits = lib.sglc_attention_decode_splits(T, n_heads, int(max_keys))
+    need_ws, need_c = ctypes.c_longlong(0), ctypes.c_int(0)
+    lib.sglc_attention_decode_scratch(T, n_heads, D, splits, ctypes.byref(need_ws), ctypes.byref(need_c))
+    if need_ws.value > ws.numel() or need_c.value > counters.numel():
+        splits = 1
+    code = lib.sglc_attention_decode_shared(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+                                            block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
+                                            out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
+                                            int(window or 0), int(max_keys), splits, _ptr(ws), _ptr(counters),
+                                            _ptr(err), _ptr(token_list), n_pages, _stream())
+    _check(lib, code, f"attention_decode_shared (head_dim {D}, up to {max_keys} keys)")
+
+
 # ---------------------------------------------------------------------------
 def attention_prefill_tc_supported(q, cache, scale):
     D = cache.shape[-1]
@@ -502,9 +576,11 @@ def attention_prefill_tc_supported(q, cache, scale):
 
 
 def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, scale, window,
-                         n_requests, max_q_len, skip_single=False):
+                         n_requests, max_q_len, skip_single=False, kv_shared=False):
     """Causal attention of prompt portions on the tensor cores (tcgen05), bfloat16, head
-    sizes 64 and 128.  q_start int32 [R+1], kv_len int32 [R] (lengths after this step)."""
+    sizes 64 and 128.  q_start int32 [R+1], kv_len int32 [R] (lengths after this step).
+    kv_shared: cache is [n_pages, 1, n_kv_heads, page_size, head_dim], rows that are keys and
+    values at once."""
     _need_cuda(q, cache, block_table, q_start, kv_len, out)
     for t, nm in ((block_table, "block_table"), (q_start, "q_start"), (kv_len, "kv_len")):
         _i32(t, nm)
@@ -515,13 +591,16 @@ def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, s
     if q.shape[1] != n_heads * D or q.stride(1) != 1 or out.stride(1) != 1 or out.dtype != torch.bfloat16 \
             or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
         raise KernelError("attention_prefill_tc: query/output rows do not match heads x head_dim")
+    if two != (1 if kv_shared else 2):
+        raise KernelError(f"attention_prefill_tc: cache {tuple(cache.shape)} does not fit kv_shared={kv_shared}")
     lib = build.load("attention_prefill_tc")
     err = _tc_buffers(q.device)[2]
-    code = lib.sglc_attention_prefill_tc(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
-                                         block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(out),
-                                         out.stride(0), int(n_requests), int(max_q_len), n_heads, Hkv, D,
-                                         page_size, ctypes.c_float(scale), int(window or 0), q.shape[0],
-                                         n_pages, 1 if skip_single else 0, _ptr(err), _stream())
+    fn = lib.sglc_attention_prefill_tc_shared if kv_shared else lib.sglc_attention_prefill_tc
+    code = fn(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+              block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(out),
+              out.stride(0), int(n_requests), int(max_q_len), n_heads, Hkv, D,
+              page_size, ctypes.c_float(scale), int(window or 0), q.shape[0],
+              n_pages, 1 if skip_single else 0, _ptr(err), _stream())
     _check(lib, code, f"attention_prefill_tc (head_dim {D})")
 
 

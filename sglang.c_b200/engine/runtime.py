@@ -105,6 +105,24 @@ class Runtime:
     def attend_shared(self, ctx, q, binding, grp, out, n_heads, head_dim, scale, window):
         """Causal attention of the step's queries over a cache whose rows are keys and values at
         once (one shared head: a latent).  The rows of the step's own tokens are in the cache
-        already (whoever owns it wrote them)."""
-        ops.attention_simt(q, binding.tensor, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
+        already (whoever owns it wrote them).  The same choice of kernel as attend(): single
+        tokens to the split-key kernel, prompt portions to the tensor cores where the head size
+        allows, everything else (and the 32-bit path) to the general kernel."""
+        cache = binding.tensor
+        bf16_ok = self.dtype == "bfloat16" and head_dim % 8 == 0 and head_dim <= 256 and q.stride(0) % 8 == 0 \
+            and q.data_ptr() % 16 == 0
+        if bf16_ok and ctx.max_q_len == 1:
+            return ops.attention_decode_shared(q, cache, grp.block_table, None, ctx.positions, out, n_heads, scale,
+                                               window, ctx.max_keys)
+        if bf16_ok and ops.attention_prefill_tc_supported(q, cache, scale) \
+                and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+            split = ctx.n_decode > 0
+            ops.attention_prefill_tc(q, cache, grp.block_table, ctx.q_start, ctx.kv_len, out, n_heads, scale, window,
+                                     ctx.R, ctx.max_q_len, skip_single=split, kv_shared=True)
+            if split:
+                ops.attention_decode_shared(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
+                                            scale, window, ctx.max_keys, token_list=ctx.decode_tokens,
+                                            n_tokens=ctx.n_decode)
+            return
+        ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
                            scale, window, ctx.max_keys, max_q_len=ctx.max_q_len, kv_shared=True)

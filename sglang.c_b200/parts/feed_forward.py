@@ -31,20 +31,27 @@ class MLP(Part):
         lay = self.params.get("weight_layout", "linear")
         self.up = Linear.from_refs(store, tensors["up_weight"], tensors.get("up_bias"), lay)
         self.down = Linear.from_refs(store, tensors["down_weight"], tensors.get("down_bias"), lay)
-        self.act_params = None
+        self.act_params = self.act_slot = None
         if self.params["activation"] == "xielu":
+            from ..csrc import ops
             pq = tensors["act_params"].tensor.double()
             sp = torch.nn.functional.softplus(pq)
             self.act_params = (float(sp[0]), 0.5 + float(sp[1]))
+            if self.rt is not None:
+                libs = ["gemm_simt"] + (["gemm_tc", "gemm_few"] if self.rt.dtype == "bfloat16" else [])
+                self.act_slot = ops.register_act_params(*self.act_params, libs)
+
+    act_params = act_slot = None
 
     def workspace_per_token(self):
         act = 4 if self.rt.dtype == "float32" else 2
-        return (act + (4 if self.act_in_own_kernel() else 0)) * self.params["inner_size"]
+        return (act + (4 if self.params["activation"] == "xielu" else 0)) * self.params["inner_size"]
 
     def act_in_own_kernel(self):
-        """An activation with numbers of its own has no epilogue in the products: the product's
-        32-bit result goes through a kernel of the activation."""
-        return self.params["activation"] == "xielu"
+        """An activation with numbers of its own is applied in the up-projection's epilogue from a
+        slot of the kernel libraries' parameter tables; only a model with more such activations
+        than slots sends the product's 32-bit result through a kernel of the activation."""
+        return self.params["activation"] == "xielu" and self.act_slot is None
 
     def forward(self, ctx, h, residual, out=None):
         from ..csrc import ops
@@ -54,6 +61,8 @@ class MLP(Part):
             z = ctx.alloc((T, self.params["inner_size"]), torch.float32)
             self.up.forward(ctx, h, out=z)
             ops.xielu(z, u, *self.act_params)
+        elif self.act_slot is not None:
+            self.up.forward(ctx, h, out=u, act=(self.params["activation"], self.act_slot))
         else:
             self.up.forward(ctx, h, out=u, act=self.params["activation"])
         return self.down.forward(ctx, u, out=out, residual=residual)

@@ -176,30 +176,52 @@ def test_attention_over_shared_rows_far_keys_and_page_borders(dtype, rank, heads
     bt = i32([table + [0] * 3])
     tol = 2e-5 if dtype == torch.float32 else 2e-2
 
-    def run(q, positions, max_q_len):
+    def run(q, positions, max_q_len, kernel="general"):
         T = len(positions)
         out = torch.empty((T, heads * rank), dtype=dtype, device=DEV)
-        ops.attention_simt(dev(q, dtype), cache, bt, i32([0] * T), i32(positions), out, heads, 1.0, None,
-                           max(positions) + 1, max_q_len=max_q_len, kv_shared=True)
+        if kernel == "general":
+            ops.attention_simt(dev(q, dtype), cache, bt, i32([0] * T), i32(positions), out, heads, 1.0, None,
+                               max(positions) + 1, max_q_len=max_q_len, kv_shared=True)
+        elif kernel == "decode":
+            ops.attention_decode_shared(dev(q, dtype), cache, bt, i32([0] * T), i32(positions), out, heads, 1.0, None,
+                                        max(positions) + 1)
+        else:
+            ops.attention_prefill_tc(dev(q, dtype), cache, bt, i32([0, T]), i32([positions[-1] + 1]), out, heads, 1.0,
+                                     None, 1, T, kv_shared=True)
         return out.float().cpu().numpy()
 
-    # random queries: a portion of the last 70 positions, and single tokens
+    kernels = ["general"]
+    if dtype == torch.bfloat16 and rank % 8 == 0:
+        kernels.append("decode")
+    portion_kernels = ["general"] + (["tensor"] if dtype == torch.bfloat16 and rank in (64, 128) else [])
+    # random queries: a portion of the last 70 positions, a portion that starts at 0, and single tokens
     q = rng.standard_normal((n, heads * rank)) * 1.5
     qr = dev(q, dtype).float().cpu().numpy().astype(np.float64)
     want = P.latent_attention(qr, cq, eye, eye, np.eye(heads * rank), heads, 1.0)
-    got = run(q[n - 70:], list(range(n - 70, n)), 70)
-    assert np.abs(got - want[n - 70:]).max() < tol
-    for p in (0, 1, page - 1, page, 2 * page + 1, n - 1):
-        assert np.abs(run(q[p:p + 1], [p], 1) - want[p:p + 1]).max() < tol
+    for kernel in portion_kernels:
+        got = run(q[n - 70:], list(range(n - 70, n)), 70, kernel)
+        assert np.abs(got - want[n - 70:]).max() < tol, kernel
+        got = run(q[:200], list(range(200)), 200, kernel)
+        assert np.abs(got - want[:200]).max() < tol, kernel
+    for kernel in kernels:
+        for p in (0, 1, page - 1, page, 2 * page + 1, n - 1):
+            assert np.abs(run(q[p:p + 1], [p], 1, kernel) - want[p:p + 1]).max() < tol, (kernel, p)
     # keys made to stand out
     for far in (0, 3, page - 1, page, 5 * page - 1, 5 * page, n - 2, n - 1):
         qf = np.tile(cq[far] * 40.0, heads)[None, :]
-        got = run(qf, [n - 1], 1)
-        assert np.abs(got - np.tile(cq[far], heads)).max() < 5e-2, far
-        if far > 0:       # and just out of sight: the query sits one place before it
-            got = run(qf, [far - 1], 1)
-            ref = P.latent_attention(np.repeat(qf, far, 0), cq[:far], eye, eye, np.eye(heads * rank), heads, 1.0)[-1]
-            assert np.abs(got - ref).max() < max(tol, 2e-2 if dtype == torch.bfloat16 else 1e-4), far
+        for kernel in kernels:
+            got = run(qf, [n - 1], 1, kernel)
+            assert np.abs(got - np.tile(cq[far], heads)).max() < 5e-2, (kernel, far)
+            if far > 0:       # and just out of sight: the query sits one place before it
+                got = run(qf, [far - 1], 1, kernel)
+                ref = P.latent_attention(np.repeat(qf, far, 0), cq[:far], eye, eye, np.eye(heads * rank), heads, 1.0)[-1]
+                assert np.abs(got - ref).max() < max(tol, 2e-2 if dtype == torch.bfloat16 else 1e-4), (kernel, far)
+        for kernel in portion_kernels[1:]:
+            # the last query of a portion points at the far key; the one before it must not see position n-1
+            qs = np.concatenate([q[n - 40:n - 1], qf])
+            got = run(qs, list(range(n - 40, n)), 40, kernel)
+            assert np.abs(got[-1] - np.tile(cq[far], heads)).max() < 5e-2, (kernel, far)
+            assert np.abs(got[:-1] - want[n - 40:n - 1]).max() < tol, (kernel, far)
 
 
 # ---------------------------------------------------------------------------- whole models
