@@ -18,7 +18,8 @@ requests) over its time, against the measured copy bandwidth; `points` has decod
 at batch 1 and 64, the true 32-bit path and the prefill through the C interface;
 `kernels` says where a decode and a
 prefill step's time goes, kernel by kernel.  `--full` adds medium and XL layer
-sizes and the mixed workload to `points`.
+sizes and the mixed workload to `points`.  `--compare tukavik` measures, instead of all
+this, a Tukavik model beside the GPT-2 model of the same layer sizes.
 """
 import argparse
 import atexit
@@ -654,6 +655,99 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
     return r
 
 
+def tukavik_config(base, n_layer):
+    """A Tukavik model with the layer sizes of a GPT-2 model: the same width, depth, feed-forward
+    width, head count and vocabulary; layers in threes: a minGRU recurrence as wide as the model, latent
+    attention (heads of 64, a latent of 128), latent attention with low-rank queries that reads the
+    latents of the layer before it."""
+    E, H, I = base["n_embd"], base["n_head"], base["n_inner"]
+    mlp = {"kind": "dense", "ff": I}
+    layers = []
+    for i in range(n_layer):
+        if i % 3 == 0:
+            layers.append({"type": "mingru", "mixer": {"width": E}, "mlp": mlp})
+        else:
+            m = {"heads": H, "dim": 64, "vdim": 64, "kv_rank": 128, "scale": 0.125}
+            if i % 3 == 2:
+                m.update(q_rank=E // 2, kv_from=i - 1)
+            layers.append({"type": "latent_attention" if i % 3 == 1 else "latent_attention_2", "mixer": m, "mlp": mlp})
+    return {"architecture": "Tukavik", "vocab": base["vocab_size"], "width": E, "norm": {"eps": 1e-5},
+            "layers": layers, "max_positions": base["n_positions"]}
+
+
+def tukavik_step_bytes(cfg, batch, context, prompt_tokens):
+    """What the kernels that only this design has must move, summed over a step's launches of each
+    (bfloat16 activations, 32-bit residual stream and states): {kernel label: (decode bytes, prefill bytes)}."""
+    E, L = cfg["width"], len(cfg["layers"])
+    out = {}
+    for name, T in (("decode", batch), ("prefill", prompt_tokens)):
+        scan = norm = depth = attn = 0
+        for i, layer in enumerate(cfg["layers"]):
+            m = layer["mixer"]
+            subs = 2 if layer["mlp"] else 1
+            norm += subs * T * E * (4 + 8)                       # the sublayer's result in, the stream read and written
+            norm += subs * T * E * (4 + 2)                       # the norm ahead of a sublayer
+            depth += T * E * 4 * (i + 2 + 2)
+            if layer["type"] == "mingru":
+                W = m["width"]
+                scan += T * W * (12 + 2) + (batch * W * 8 if name == "decode" else T * W * 8)
+            else:
+                R, H = m["kv_rank"], m["heads"]
+                norm += T * R * (4 + 2) * (1 if "kv_from" in m else 1) + (T * m.get("q_rank", 0) * 6)
+                # every query reads the latents of its context once (decode), or a tile of 128 queries does (prefill)
+                keys = batch * context if name == "decode" else 2 * sum(range(1, prompt_tokens // 2 // 128 + 1)) * 128
+                attn += keys * R * 2 + T * H * R * 4
+        out[name] = {"mingru_scan": scan, "norm_rows": norm, "depth_mix": depth, "attention_shared": attn}
+    return out
+
+
+def compare_tukavik(sizes, steps, warmup, pk):
+    """Decode (batch 8 and 64 at context 512) and prefill (2 x 1,024 tokens) of a Tukavik model beside
+    the GPT-2 model of the same layer sizes, both through the Python engine's step function (the
+    native engine runs GPT-2's parts only), bfloat16, random weights; and each model's kernel table."""
+    import torch
+    from sglang_c_b200.config import resolve_architecture
+    from sglang_c_b200.engine import Engine
+    from sglang_c_b200.weights import write_random_model
+    res = {}
+    for size in sizes:
+        base = MODELS[size]
+        n_layer = base["n_layer"]
+        row = {}
+        for design in ("gpt2", "tukavik"):
+            tmp = tempfile.mkdtemp(prefix="sglc_bench_")
+            atexit.register(shutil.rmtree, tmp, True)
+            cfg_d = dict(base) if design == "gpt2" else tukavik_config(base, n_layer)
+            arch = resolve_architecture(cfg_d)
+            model_dir = write_random_model(os.path.join(tmp, "model"), arch, arch.config_class.from_dict(cfg_d), 1234,
+                                           scheme="standard", store_dtype="bfloat16")
+            eng = Engine.from_dir(model_dir, dtype="bfloat16", page_size=PAGE, max_tokens=64 * (CONTEXT + 256),
+                                  max_requests=64, max_step_tokens=PREFILL_TOKENS)
+            time_decode(eng, BATCH, 32, 2, 3)
+            r = {"weight_bytes": eng.model.weight_bytes}
+            for b in (8, 64):
+                ms, launches, _ = time_decode(eng, b, CONTEXT, steps, warmup)
+                r[f"decode_b{b}"] = {"tok_s": b / (ms / 1e3), "ms": ms, "launches_per_step": launches / steps}
+            dms = time_prefill(eng, 2, PREFILL_TOKENS // 2, 3, behind_sleep=True)
+            r["prefill"] = {"tok_s": PREFILL_TOKENS / (dms / 1e3), "device_ms": dms}
+            r["kernels"] = kernel_table(eng, BATCH, CONTEXT, PREFILL_TOKENS // 2)
+            if design == "tukavik":
+                nb = tukavik_step_bytes(cfg_d, BATCH, CONTEXT, PREFILL_TOKENS)
+                for kind in ("decode", "prefill"):
+                    for label, k in r["kernels"][kind].items():
+                        key = {"mingru_scan": "mingru_scan", "norm_rows": "norm_rows", "depth_mix": "depth_mix",
+                               "attention_decode_shared": "attention_shared"}.get(label)
+                        if key and k["us"] > 0:
+                            k["bytes"] = nb[kind][key]
+                            k["frac_of_copy"] = round(nb[kind][key] / (k["us"] * 1e-6) / 1e9 / pk["hbm_gbs"], 4)
+            row[design] = r
+            del eng
+            torch.cuda.empty_cache()
+            shutil.rmtree(tmp, True)
+        res[size] = row
+    return res
+
+
 def only(kind, base, n_layer, steps, warmup, batch=BATCH):
     """A handful of steps of one kind, each run as its launches (no graph: a profiler then sees
     the kernels in launch order), and one line of JSON with their device time."""
@@ -731,6 +825,9 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "fp32"],
                     help="a handful of steps of one kind and nothing else (what a profiler is pointed at): "
                          "decode steps at batch 8, prefill steps of 2 x 1,024 tokens, or both on the 32-bit path")
+    ap.add_argument("--compare", default=None, choices=["tukavik"],
+                    help="nothing of the above: decode and prefill of a model of this design beside the GPT-2 model "
+                         "of equal layer sizes (--model, or small and medium with --full), with both kernel tables")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_main(args)
@@ -745,6 +842,15 @@ def main():
     n_layer = args.layers or base["n_layer"]
     if args.only:
         return only(args.only, base, n_layer, steps, warmup, args.batch)
+    if args.compare:
+        clocks = ClockSampler()
+        clocks.start()
+        res = compare_tukavik(["small", "medium"] if args.full else [args.model], steps, warmup, pk)
+        print(json.dumps({"metric": "decode and prefill tok/s, Tukavik beside GPT-2 at equal layer sizes (Python engine)",
+                          "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "steps": steps, "warmup": warmup,
+                          "data": "synthetic: seeded random weights and uniform random token ids",
+                          "peaks": pk, "sizes": res, "clocks": clocks.stop()}))
+        return 0
     if args.workload == "mixed":
         tmp = tempfile.mkdtemp(prefix="sglc_bench_")
         atexit.register(shutil.rmtree, tmp, True)

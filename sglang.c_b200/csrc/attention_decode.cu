@@ -181,7 +181,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
       const __nv_bfloat16* krow =
           cache + (size_t)spage[p / page_size] * page_elems + head_off + (size_t)(p % page_size) * D;
       kpre[x] = __ldg(reinterpret_cast<const uint4*>(krow) + dl);
-      vpre[x] = __ldg(reinterpret_cast<const uint4*>(krow + v_off) + dl);
+      vpre[x] = kv_shared ? kpre[x] : __ldg(reinterpret_cast<const uint4*>(krow + v_off) + dl);   // (shared rows: one load)
     }
   }
   pdl_wait();
@@ -197,7 +197,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
       const __nv_bfloat16* vrow = fused ? vn : krow + v_off;
       // plain loads: this data was written by the kernel ahead, not before the step
       kpre[x] = *(reinterpret_cast<const uint4*>(krow) + dl);
-      vpre[x] = *(reinterpret_cast<const uint4*>(vrow) + dl);
+      vpre[x] = kv_shared ? kpre[x] : *(reinterpret_cast<const uint4*>(vrow) + dl);
     }
   }
   // the token's own key and value into the cache (one head of a group does it)

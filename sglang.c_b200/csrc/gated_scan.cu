@@ -10,18 +10,19 @@
 // enters the recurrence is 32-bit.  A request's tokens lie together (q_start[r] .. q_start[r+1]);
 // its state is state[state_slots[r]][:], read at its first token and written back after its last.
 //
-// Two ways through a step.  Steps whose longest portion fits one chunk: one launch, a thread a
-// (request, channel), the tokens one after the other.  Longer portions: the recurrence
-// S_out = A S_in + B of a chunk of tokens composes, so a first launch reduces every chunk of
-// CHUNK tokens to its (A, B) from a zero state, and a second launch starts every chunk from
-// the state that the chunks ahead of it compose to and writes the outputs; chunks run side by
+// Two ways through a step.  Steps whose longest portion has at most CHUNK tokens: one launch, a
+// thread a (request, channel), the tokens one after the other.  Longer portions: the recurrence
+// S_out = A S_in + B of a piece of tokens composes, so a first launch reduces every piece of
+// PIECE tokens to its (A, B) from a zero state, and a second launch starts every piece from
+// the state that the pieces ahead of it compose to and writes the outputs; pieces run side by
 // side.  The two ways differ in the rounding of the state only.
 #include "common.cuh"
 
 SGLC_DEFINE_ERROR_STRING()
 
 constexpr int SCAN_THREADS = 128;
-constexpr int SCAN_CHUNK = 128;
+constexpr int SCAN_CHUNK = 128;   // a step goes the chunked way when its longest portion exceeds this
+constexpr int SCAN_PIECE = 32;    // tokens of one block of the chunked way (more blocks than with whole chunks)
 
 __device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float mingru_candidate(float u) { return u >= 0.0f ? u + 0.5f : sigmoid_f32(u); }
@@ -37,16 +38,16 @@ struct ScanArgs {
   const int* q_start;      // [R+1]
   const int* state_slots;  // [R]
   int R, W, n_slots, n_chunks;
-  float* ws_a;             // chunked way: [T / CHUNK + R][W] each (see chunk_row), and [R][W] of incoming states
+  float* ws_a;             // chunked way: [T / PIECE + R][W] each (see chunk_row), and [R][W] of incoming states
   float* ws_b;
   float* ws_s0;
   int* err;
 };
 
-// Where the chunk that starts at token t0 of the step's r-th request keeps its (A, B): chunks of
-// one request start CHUNK tokens apart and a later request's tokens come later, so
-// t0 / CHUNK + r grows by at least one from any chunk to the next and stays below T / CHUNK + R.
-__device__ __forceinline__ size_t chunk_row(int t0, int r) { return (size_t)(t0 / SCAN_CHUNK + r); }
+// Where the piece that starts at token t0 of the step's r-th request keeps its (A, B): pieces of
+// one request start PIECE tokens apart and a later request's tokens come later, so
+// t0 / PIECE + r grows by at least one from any piece to the next and stays below T / PIECE + R.
+__device__ __forceinline__ size_t chunk_row(int t0, int r) { return (size_t)(t0 / SCAN_PIECE + r); }
 
 template <typename TO>
 __global__ void __launch_bounds__(SCAN_THREADS)
@@ -91,7 +92,7 @@ mingru_chunk_reduce_kernel(ScanArgs p) {
   if (ch >= p.W) return;
   pdl_wait();
   const int q0 = p.q_start[r], q1 = p.q_start[r + 1];
-  const int t0 = q0 + c * SCAN_CHUNK, t1 = min(t0 + SCAN_CHUNK, q1);
+  const int t0 = q0 + c * SCAN_PIECE, t1 = min(t0 + SCAN_PIECE, q1);
   if (t0 >= q1) return;
   if (c == 0) {
     const int slot = p.state_slots[r];
@@ -129,11 +130,11 @@ mingru_chunk_apply_kernel(ScanArgs p) {
   if (ch >= p.W) return;
   pdl_wait();
   const int q0 = p.q_start[r], q1 = p.q_start[r + 1];
-  const int t0 = q0 + c * SCAN_CHUNK, t1 = min(t0 + SCAN_CHUNK, q1);
+  const int t0 = q0 + c * SCAN_PIECE, t1 = min(t0 + SCAN_PIECE, q1);
   if (t0 >= q1) return;
   float S = p.ws_s0[(size_t)r * p.W + ch];
   for (int k = 0; k < c; k++) {
-    const size_t w = chunk_row(q0 + k * SCAN_CHUNK, r) * p.W + ch;
+    const size_t w = chunk_row(q0 + k * SCAN_PIECE, r) * p.W + ch;
     S = fmaf(p.ws_a[w], S, p.ws_b[w]);
   }
   TO* y = reinterpret_cast<TO*>(p.y);
@@ -163,12 +164,13 @@ mingru_chunk_apply_kernel(ScanArgs p) {
 }
 
 SGLC_API int sglc_gated_scan_chunk() { return SCAN_CHUNK; }
+SGLC_API int sglc_gated_scan_piece() { return SCAN_PIECE; }
 
 // Floats of workspace the chunked way takes for a step of T tokens in R requests whose longest
 // portion has max_q_len tokens (0: the step goes the one-launch way and needs none).
 SGLC_API long long sglc_mingru_scan_workspace(int R, int W, int T, int max_q_len) {
   if (max_q_len <= SCAN_CHUNK) return 0;
-  return (long long)W * (2LL * (T / SCAN_CHUNK + R) + R);
+  return (long long)W * (2LL * (T / SCAN_PIECE + R) + R);
 }
 
 // a, u, g: float, rows in_stride apart; y: [T][y_stride] of y_dtype; state: [n_slots][W] float;
@@ -194,9 +196,10 @@ SGLC_API int sglc_mingru_scan(const float* a, const float* u, const float* g, lo
     return sglc_launch(mingru_scan_kernel<__nv_bfloat16>, grid, dim3(SCAN_THREADS), 0, stream, 1, true, p);
   }
   if (!ws) return SGLC_ERR_ARGUMENT;
-  p.n_chunks = (max_q_len + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  // (the grid depends on the longest portion in whole chunks only, as a captured graph's key does)
+  p.n_chunks = (max_q_len + SCAN_CHUNK - 1) / SCAN_CHUNK * (SCAN_CHUNK / SCAN_PIECE);
   if (p.n_chunks > 65535 || cb > 65535) return SGLC_ERR_UNSUPPORTED;
-  const size_t rows = (size_t)(T / SCAN_CHUNK + R);
+  const size_t rows = (size_t)(T / SCAN_PIECE + R);
   p.ws_a = ws;
   p.ws_b = ws + rows * W;
   p.ws_s0 = ws + 2 * rows * W;

@@ -305,7 +305,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         if (e < BN) s_bias[e] = (a.bias && qt * BN + e < a.N) ? a.bias[qt * BN + e] : 0.0f;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int row = lane_base + lane;
-        const bool to_f32 = a.residual != nullptr;
+        const bool to_f32 = a.residual != nullptr || a.out_f32;      // float boxes: added into the stream, or stored
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -337,9 +337,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         fence_async_proxy();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64) {
-          if (to_f32) {
+          if (a.residual) {
             for (int b = 0; b < BN / 32; b++)
               tma_reduce_add_2d(&map_out, smem + (size_t)b * (BM * 128), qt * BN + b * 32, pt * BM);
+          } else if (to_f32) {
+            for (int b = 0; b < BN / 32; b++)
+              tma_store_2d(&map_out, smem + (size_t)b * (BM * 128), qt * BN + b * 32, pt * BM);
           } else {
             for (int b = 0; b < BN / 64; b++)
               tma_store_2d(&map_out, smem + (size_t)b * (BM * 128), qt * BN + b * 64, pt * BM);
@@ -597,7 +600,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int e = threadIdx.x - 64;
     const int lane_base = (warp & 3) * 32;
     const int row = lane_base + lane;
-    const bool to_f32 = a.residual != nullptr;
+    const bool to_f32 = a.residual != nullptr || a.out_f32;      // float boxes: added into the stream, or stored
     const int box_cols = to_f32 ? 32 : 64;
     int n = 0, boxes = 0;
     bool ok = true;
@@ -686,7 +689,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (threadIdx.x == 64) {
               const int x0 = qt * BN + (c + 32 - box_cols);
-              if (to_f32) tma_reduce_add_2d(&map_out, box, x0, pt * BM);
+              if (a.residual) tma_reduce_add_2d(&map_out, box, x0, pt * BM);
               else tma_store_2d(&map_out, box, x0, pt * BM);
               tma_store_commit();
             }
@@ -871,7 +874,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int bar_id = 1 + grp, c_lo = grp * GC;
     const int lane_base = (warp & 3) * 32;
     const int row = lane_base + lane;
-    const bool to_f32 = a.residual != nullptr;
+    const bool to_f32 = a.residual != nullptr || a.out_f32;      // float boxes: added into the stream, or stored
     const int box_cols = to_f32 ? 32 : 64;
     uint8_t* box = epi + (size_t)grp * BOX_BYTES;
     int n = 0;
@@ -960,7 +963,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             named_bar_sync(bar_id, 128);
             if (leader) {
               const int x0 = qt * BN + (c + 32 - box_cols);
-              if (to_f32) tma_reduce_add_2d(&map_out, box, x0, pt * BM);
+              if (a.residual) tma_reduce_add_2d(&map_out, box, x0, pt * BM);
               else tma_store_2d(&map_out, box, x0, pt * BM);
               tma_store_commit();
             }
@@ -1045,7 +1048,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mo, 
   }
   if (a.tma_out) {
     // the outgoing tile is staged in the stage buffers: 16 KB per 128-byte-wide box
-    size_t need = (size_t)(a.residual ? BN / 32 : BN / 64) * BM * 128 + 1024;
+    size_t need = (size_t)((a.residual || a.out_f32) ? BN / 32 : BN / 64) * BM * 128 + 1024;
     if (smem < need) smem = need;
   }
   return sglc_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, mo, a);
@@ -1249,7 +1252,8 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
   a.tma_out = 0;
   if (!swap && bn >= 64) {
     if (residual) a.tma_out = get_map(&mo, residual, M, N, ldo, BM | 0x10000u) ? 1 : 0;
-    else if (!out_f32) a.tma_out = get_map(&mo, out, M, N, ldo, BM) ? 1 : 0;
+    else if (out_f32) a.tma_out = get_map(&mo, out, M, N, ldo, BM | 0x10000u) ? 1 : 0;
+    else a.tma_out = get_map(&mo, out, M, N, ldo, BM) ? 1 : 0;
   }
   if (kv) {
     // only the many-token kernels scatter: 32-column chunks within a head, the queries' last

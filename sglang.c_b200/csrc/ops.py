@@ -662,15 +662,16 @@ def norm_rows(src, gain, bias, eps, dst, form="layer", add=False, dst_rows=None,
     _check(lib, code, f"norm_rows (width {E})")
 
 
-GATED_SCAN_CHUNK = 128      # tokens per chunk of the gated scans' chunked way (gated_scan.cu: SCAN_CHUNK)
+GATED_SCAN_CHUNK = 128      # a step whose longest portion exceeds this goes the gated scans' chunked way ...
+GATED_SCAN_PIECE = 32       # ... in pieces of so many tokens a block (gated_scan.cu: SCAN_CHUNK, SCAN_PIECE)
 
 
 def mingru_scan_workspace(n_requests, width, n_tokens, max_q_len):
     """Floats of workspace mingru_scan needs for such a step: none while the longest portion fits
-    one chunk, else two per channel and chunk row plus one per channel and request."""
+    one chunk, else two per channel and piece row plus one per channel and request."""
     if max_q_len <= GATED_SCAN_CHUNK:
         return 0
-    return int(width) * (2 * (int(n_tokens) // GATED_SCAN_CHUNK + int(n_requests)) + int(n_requests))
+    return int(width) * (2 * (int(n_tokens) // GATED_SCAN_PIECE + int(n_requests)) + int(n_requests))
 
 
 def mingru_scan(gate, cand, out_gate, y, state, q_start, state_slots, n_requests, max_q_len, workspace=None):
@@ -692,7 +693,7 @@ def mingru_scan(gate, cand, out_gate, y, state, q_start, state_slots, n_requests
     if need and (workspace is None or workspace.dtype != torch.float32 or workspace.numel() < need):
         raise KernelError(f"mingru_scan: a step with portions of {max_q_len} tokens needs {need} floats of workspace")
     lib = build.load("gated_scan")
-    if lib.sglc_gated_scan_chunk() != GATED_SCAN_CHUNK:
+    if lib.sglc_gated_scan_chunk() != GATED_SCAN_CHUNK or lib.sglc_gated_scan_piece() != GATED_SCAN_PIECE:
         raise KernelError("gated_scan: the library's chunk size differs from the binding's")
     code = lib.sglc_mingru_scan(_ptr(gate), _ptr(cand), _ptr(out_gate), ctypes.c_longlong(gate.stride(0)), _ptr(y),
                                 ctypes.c_longlong(y.stride(0)), _dt(y, "scan output"), _ptr(state), state.shape[0],

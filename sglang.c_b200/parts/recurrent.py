@@ -45,7 +45,7 @@ class MinGRU(Part):
         # floats a channel for every chunk's worth of tokens and three for every request, of
         # which a step has no more than tokens
         W = self.params["width"]
-        return W * (12 + act) + 12 * W + 8 * W // ops.GATED_SCAN_CHUNK + 8
+        return W * (12 + act) + 12 * W + 8 * W // ops.GATED_SCAN_PIECE + 8
 
     def forward(self, ctx, h, residual, cache, position=None, out=None):
         T, W = h.shape[0], self.params["width"]
