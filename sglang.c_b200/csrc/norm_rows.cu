@@ -41,7 +41,7 @@ __global__ void norm_rows_kernel(const TI* __restrict__ src, long long src_strid
   float q = 0.0f;
   for (int i = threadIdx.x; i < E; i += blockDim.x) {
     const float d = srow[i] - mean;
-    q += d * d;
+    q = fmaf(d, d, q);
   }
   const float inv = 1.0f / sqrtf(block_sum(q, red) / (float)E + eps);
   long long row = r;
@@ -51,12 +51,110 @@ __global__ void norm_rows_kernel(const TI* __restrict__ src, long long src_strid
   }
   TO* o = dst + (size_t)row * dst_stride;
   for (int i = threadIdx.x; i < E; i += blockDim.x) {
-    float y = (srow[i] - mean) * inv;
-    if (gain) y *= gain[i];
-    if (bias) y += bias[i];
-    if (ADD) o[i] = from_f32<TO>(to_f32(o[i]) + y);
+    // (explicit roundings: the fused tail below must give the same bits, whatever either compiles to)
+    float y = __fmul_rn(srow[i] - mean, inv);
+    if (gain) y = __fmul_rn(y, gain[i]);
+    if (bias) y = __fadd_rn(y, bias[i]);
+    if (ADD) o[i] = from_f32<TO>(__fadd_rn(to_f32(o[i]), y));
     else o[i] = from_f32<TO>(y);
   }
+}
+
+// The tail of a sublayer in one launch, a block a row:
+//   x += norm_post(y) * g_post                                   (x: the 32-bit stream)
+//   [mix]   hist[n_terms-1] = x;  x = sum_j w[j] * hist[j]        (a depth-weighted average, j ascending)
+//   [next]  h = norm_next(x) * g_next                            (the norm ahead of the next sublayer)
+// The same arithmetic in the same order as the three kernels it stands for, so the bits are theirs.
+template <typename TO>
+__global__ void norm_add_tail_kernel(const float* __restrict__ y, long long y_stride,
+                                     const float* __restrict__ g_post, float eps_post, int form_post,
+                                     float* __restrict__ x, float* __restrict__ hist, long long hist_block,
+                                     int n_terms, const float* __restrict__ mix_w,
+                                     const float* __restrict__ g_next, float eps_next, int form_next,
+                                     TO* __restrict__ h, long long h_stride, int n_rows, int E) {
+  extern __shared__ float srow[];   // E floats
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* yr = y + (size_t)r * y_stride;
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float v = yr[i];
+    srow[i] = v;
+    s += v;
+  }
+  float mean = 0.0f;
+  if (form_post == NORM_LAYER) mean = block_sum(s, red) / (float)E;
+  else __syncthreads();
+  float q = 0.0f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float d = srow[i] - mean;
+    q = fmaf(d, d, q);
+  }
+  float inv = 1.0f / sqrtf(block_sum(q, red) / (float)E + eps_post);
+  float* xr = x + (size_t)r * E;
+  s = 0.0f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    float v = __fmul_rn(srow[i] - mean, inv);
+    if (g_post) v = __fmul_rn(v, g_post[i]);
+    v = __fadd_rn(xr[i], v);
+    if (n_terms > 0) {
+      const size_t at = (size_t)r * E + i;
+      hist[(size_t)(n_terms - 1) * hist_block + at] = v;
+      if (n_terms > 1) {
+        float acc = 0.0f;
+        for (int j = 0; j < n_terms - 1; j++) acc = fmaf(mix_w[j], hist[(size_t)j * hist_block + at], acc);
+        v = fmaf(mix_w[n_terms - 1], v, acc);
+      }
+    }
+    xr[i] = v;
+    srow[i] = v;
+    s += v;
+  }
+  if (!h) return;
+  mean = 0.0f;
+  if (form_next == NORM_LAYER) mean = block_sum(s, red) / (float)E;
+  else __syncthreads();
+  q = 0.0f;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    const float d = srow[i] - mean;
+    q = fmaf(d, d, q);
+  }
+  inv = 1.0f / sqrtf(block_sum(q, red) / (float)E + eps_next);
+  TO* hr = h + (size_t)r * h_stride;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    float v = __fmul_rn(srow[i] - mean, inv);
+    if (g_next) v = __fmul_rn(v, g_next[i]);
+    hr[i] = from_f32<TO>(v);
+  }
+}
+
+// y: float [n_rows][y_stride]; x: float [n_rows][E] contiguous; hist (n_terms > 0): float blocks of
+// hist_block elements, block j holding [n_rows][E]; h (may be null): [n_rows][h_stride] of h_dtype.
+SGLC_API int sglc_norm_add_tail(const float* y, long long y_stride, const float* g_post, float eps_post,
+                                int form_post, float* x, float* hist, long long hist_block, int n_terms,
+                                const float* mix_w, const float* g_next, float eps_next, int form_next, void* h,
+                                long long h_stride, int h_dtype, int n_rows, int E, cudaStream_t stream) {
+  if (n_rows <= 0) return SGLC_OK;
+  if (E <= 0 || n_terms < 0 || (n_terms > 0 && !hist) || (n_terms > 1 && !mix_w)) return SGLC_ERR_ARGUMENT;
+  const size_t smem = (size_t)E * sizeof(float);
+  if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
+  const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : (E >= 128 ? 128 : (E >= 64 ? 64 : 32)));
+  if (h && h_dtype == SGLC_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_add_tail_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return sglc_launch(norm_add_tail_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, 1, true, y,
+                       y_stride, g_post, eps_post, form_post, x, hist, hist_block, n_terms, mix_w, g_next, eps_next,
+                       form_next, (__nv_bfloat16*)h, h_stride, n_rows, E);
+  }
+  if (h && h_dtype != SGLC_F32) return SGLC_ERR_ARGUMENT;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(norm_add_tail_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return sglc_launch(norm_add_tail_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, 1, true, y, y_stride,
+                     g_post, eps_post, form_post, x, hist, hist_block, n_terms, mix_w, g_next, eps_next, form_next,
+                     (float*)h, h_stride, n_rows, E);
 }
 
 // form: 0 layer, 1 RMS.  src_rows: null, or the source row of every output row (a gather).  src_dtype/dst_dtype: SGLC_F32 or SGLC_BF16.  dst_rows: null, or the

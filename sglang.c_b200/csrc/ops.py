@@ -568,6 +568,47 @@ def attention_decode_shared(q, cache, block_table, token_req, positions, out, n_
     _check(lib, code, f"attention_decode_shared (head_dim {D}, up to {max_keys} keys)")
 
 
+def attention_latent_decode_supported(q, cache, n_heads):
+    """Whether the all-heads-a-block kernel takes this cache and these queries."""
+    n_pages, one, Hkv, page_size, D = cache.shape
+    return (one == 1 and Hkv == 1 and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+            and bool(build.load("attention_latent").sglc_attention_latent_decode_supports(int(n_heads), int(D))))
+
+
+def attention_latent_decode(q, cache, block_table, token_req, positions, out, n_heads, scale, window, max_keys,
+                            token_list=None, n_tokens=None, n_splits=None):
+    """Attention of single decoded tokens over a cached latent [n_pages, 1, 1, page_size, D] (rows
+    that are keys and values of every head): one block serves all heads of a token over a range
+    of its keys, so a row comes from memory once.  token_req None: token t belongs to the step's
+    t-th request.  token_list (int32, its first n_tokens entries): the tokens to serve."""
+    _need_cuda(q, cache, block_table, token_req, positions, out, token_list)
+    for t, nm in ((block_table, "block_table"), (positions, "positions")):
+        _i32(t, nm)
+    T = q.shape[0]
+    if token_req is not None:
+        _i32(token_req, "token_req")
+    if token_list is not None:
+        _i32(token_list, "token_list")
+        T = int(n_tokens)
+    n_pages, one, Hkv, page_size, D = cache.shape
+    if one != 1 or Hkv != 1 or not cache.is_contiguous() or cache.dtype != torch.bfloat16 \
+            or q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_latent_decode: bfloat16 queries and output, cache [n_pages,1,1,page,dim]")
+    if q.shape[1] != n_heads * D or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention_latent_decode: query/output rows do not match heads x dim")
+    lib = build.load("attention_latent")
+    ws, _, err = _tc_buffers(q.device)
+    splits = int(n_splits) if n_splits else lib.sglc_attention_latent_decode_splits(T, int(max_keys))
+    if splits > 1 and T * splits * n_heads * (D + 2) > ws.numel():
+        splits = 1
+    code = lib.sglc_attention_latent_decode(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+                                            block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(token_list),
+                                            _ptr(out), out.stride(0), T, n_heads, D, page_size, ctypes.c_float(scale),
+                                            int(window or 0), splits, _ptr(ws), ctypes.c_longlong(ws.numel()), n_pages,
+                                            _ptr(err), _stream())
+    _check(lib, code, f"attention_latent_decode (dim {D}, up to {max_keys} keys)", n_kernels=2 if splits > 1 else 1)
+
+
 # ---------------------------------------------------------------------------
 def attention_prefill_tc_supported(q, cache, scale):
     D = cache.shape[-1]
@@ -660,6 +701,33 @@ def norm_rows(src, gain, bias, eps, dst, form="layer", add=False, dst_rows=None,
                               _ptr(dst_rows), ctypes.c_longlong(dst.shape[0]), n, E, ctypes.c_float(eps),
                               NORM_FORMS[form], 1 if add else 0, _ptr(tc_error_flag(src.device)), _stream())
     _check(lib, code, f"norm_rows (width {E})")
+
+
+def norm_add_tail(y, gain, eps, x, form="layer", mix=None, then=None):
+    """x += norm(y) * gain (x: float32 [T,E], the residual stream; y float32 [T,E]); then, in the same
+    launch, mix = (hist, n_terms, weights): hist[n_terms-1] = x, x = sum_j weights[j] * hist[j]
+    (as depth_mix), and then = (gain, eps, form, out): out = norm(x) * gain (the norm ahead of the
+    next sublayer).  The bits are those of the separate kernels."""
+    hist, n_terms, weights = mix if mix is not None else (None, 0, None)
+    g2, eps2, form2, out = then if then is not None else (None, 0.0, "layer", None)
+    _need_cuda(y, gain, x, hist, weights, g2, out)
+    n, E = y.shape
+    if y.dtype != torch.float32 or x.dtype != torch.float32 or y.stride(1) != 1 or not x.is_contiguous() \
+            or x.shape[1] != E or x.shape[0] < n:
+        raise KernelError("norm_add_tail: y and x are float32 [T,E], x contiguous")
+    if hist is not None and (hist.dtype != torch.float32 or not hist.is_contiguous() or hist.shape[0] < n_terms
+                             or tuple(hist.shape[1:]) != (n, E)):
+        raise KernelError("norm_add_tail: hist is float32 [>= n_terms, T, E] for this step's T")
+    if out is not None and (tuple(out.shape) != (n, E) or out.stride(1) != 1):
+        raise KernelError("norm_add_tail: the next norm's output is [T,E]")
+    lib = build.load("norm_rows")
+    code = lib.sglc_norm_add_tail(_ptr(y), ctypes.c_longlong(y.stride(0)), _ptr(gain), ctypes.c_float(eps),
+                                  NORM_FORMS[form], _ptr(x), _ptr(hist),
+                                  ctypes.c_longlong(n * E), int(n_terms), _ptr(weights), _ptr(g2),
+                                  ctypes.c_float(eps2), NORM_FORMS[form2], _ptr(out),
+                                  ctypes.c_longlong(out.stride(0) if out is not None else 0),
+                                  _dt(out, "norm output") if out is not None else F32, n, E, _stream())
+    _check(lib, code, f"norm_add_tail (width {E})")
 
 
 GATED_SCAN_CHUNK = 128      # a step whose longest portion exceeds this goes the gated scans' chunked way ...

@@ -111,18 +111,20 @@ class Runtime:
         cache = binding.tensor
         bf16_ok = self.dtype == "bfloat16" and head_dim % 8 == 0 and head_dim <= 256 and q.stride(0) % 8 == 0 \
             and q.data_ptr() % 16 == 0
+        # single tokens: all heads of a token in one block when the sizes allow (a row is read once,
+        # not once per head), else a block per (token, head)
+        one_block = bf16_ok and ops.attention_latent_decode_supported(q, cache, n_heads)
+        single = ops.attention_latent_decode if one_block else ops.attention_decode_shared
         if bf16_ok and ctx.max_q_len == 1:
-            return ops.attention_decode_shared(q, cache, grp.block_table, None, ctx.positions, out, n_heads, scale,
-                                               window, ctx.max_keys)
+            return single(q, cache, grp.block_table, None, ctx.positions, out, n_heads, scale, window, ctx.max_keys)
         if bf16_ok and ops.attention_prefill_tc_supported(q, cache, scale) \
                 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
             split = ctx.n_decode > 0
             ops.attention_prefill_tc(q, cache, grp.block_table, ctx.q_start, ctx.kv_len, out, n_heads, scale, window,
                                      ctx.R, ctx.max_q_len, skip_single=split, kv_shared=True)
             if split:
-                ops.attention_decode_shared(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
-                                            scale, window, ctx.max_keys, token_list=ctx.decode_tokens,
-                                            n_tokens=ctx.n_decode)
+                single(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads, scale, window,
+                       ctx.max_keys, token_list=ctx.decode_tokens, n_tokens=ctx.n_decode)
             return
         ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
                            scale, window, ctx.max_keys, max_q_len=ctx.max_q_len, kv_shared=True)

@@ -59,13 +59,19 @@ class SandwichNormBlock(Part):
         inner = ctx.mark()
         layer.mixer.forward(ctx, h, residual=None, cache=cache, position=position, out=y)
         ctx.release(inner)
-        layer.norm1b.add_into(ctx, y, x)
-        if "ffn" in layer.parts:
-            layer.norm2.forward(ctx, x, h)
+        # the norm behind a sublayer takes the next step along in its launch: the norm ahead of the
+        # feed-forward, or (behind the layer's last sublayer) the depth mix
+        has_ffn = "ffn" in layer.parts
+        terms = mix.terms(ctx) if mix is not None else None
+        done = layer.norm1b.add_into(ctx, y, x, then=(layer.norm2, h) if has_ffn else None,
+                                     mix=None if has_ffn else terms)
+        if has_ffn:
+            if not done:
+                layer.norm2.forward(ctx, x, h)
             layer.ffn.forward(ctx, h, residual=None, out=y)
             ctx.release(inner)
-            layer.norm2b.add_into(ctx, y, x)
+            done = layer.norm2b.add_into(ctx, y, x, mix=terms)
         ctx.release(mark)
-        if mix is not None:
+        if mix is not None and not done:
             mix.finish(ctx, x)
         return x

@@ -33,11 +33,21 @@ class LayerNorm(Part):
                           src_rows=rows)
         return out
 
-    def add_into(self, ctx, y, residual):
-        """residual += norm(y): the norm behind a sublayer, summed into the 32-bit stream."""
-        ops.norm_rows(y, self.weight, self.bias, float(self.params["eps"]), residual[:y.shape[0]],
-                      form=self.form, add=True)
-        return residual
+    def add_into(self, ctx, y, residual, mix=None, then=None):
+        """residual += norm(y): the norm behind a sublayer, summed into the 32-bit stream.  In the
+        same launch, if asked: `mix` = (hist, n_terms, weights), the depth mix of the summed rows
+        (see ops.depth_mix), and `then` = (norm part, out): out = that norm of the rows as they
+        then are (the norm ahead of the next sublayer).  Returns which of the two it did: a norm
+        with a bias, or a source that is not 32-bit, leaves them to the caller."""
+        fused = y.dtype == residual.dtype and self.bias is None and (then is None or then[0].bias is None) \
+            and y.shape[0] == residual.shape[0] and residual.is_contiguous() and (mix is not None or then is not None)
+        if not fused:
+            ops.norm_rows(y, self.weight, self.bias, float(self.params["eps"]), residual[:y.shape[0]],
+                          form=self.form, add=True)
+            return False
+        nxt = None if then is None else (then[0].weight, float(then[0].params["eps"]), then[0].form, then[1])
+        ops.norm_add_tail(y, self.weight, float(self.params["eps"]), residual, form=self.form, mix=mix, then=nxt)
+        return True
 
     def scatter(self, ctx, y, dst, dst_rows):
         """dst[dst_rows[r], :] = norm(y[r, :]): normalised rows straight into a cache's rows."""

@@ -31,6 +31,11 @@ class DepthWeightedAverage(Part):
             ctx.shared["depth_streams"] = hist
             ops.depth_mix(x, hist, 1, None)
 
+    def terms(self, ctx):
+        """(streams kept so far, terms of this layer's sum, its weights): for a kernel that does
+        the mix itself, in place of finish()."""
+        return ctx.shared["depth_streams"], self.params["index"] + 2, self.weights
+
     def finish(self, ctx, x):
         ops.depth_mix(x, ctx.shared["depth_streams"], self.params["index"] + 2, self.weights)
         return x

@@ -102,6 +102,41 @@ def test_xielu_and_depth_mix():
             assert np.abs(hist[i + 1].cpu().numpy() - new).max() < 1e-6
 
 
+@pytest.mark.parametrize("width", [10, 192, 600])
+def test_sublayer_tail_in_one_launch_has_the_bits_of_its_three_kernels(width):
+    """x += norm(y) g; the depth mix; the next norm: fused, against the plain functions and, bit
+    for bit, against the separate kernels."""
+    from sglang_c_b200.csrc import ops
+    rng = np.random.default_rng(width)
+    T, eps, n_terms = 7, 1e-5, 4
+    y, x0 = rng.standard_normal((T, width)) * 2, rng.standard_normal((T, width))
+    g1, g2, w = rng.standard_normal(width) + 1, rng.standard_normal(width) + 1, rng.standard_normal(n_terms)
+    old = [rng.standard_normal((T, width)) for _ in range(n_terms - 1)]
+    summed = x0 + P.layer_norm(y, g1, eps)
+    mixed = P.depth_average(old + [summed], w)
+    for with_mix in (False, True):
+        for out_dtype in (None, torch.float32, torch.bfloat16):
+            hist = torch.zeros((n_terms + 1, T, width), dtype=torch.float32, device=DEV)
+            hist[:n_terms - 1] = dev(np.stack(old))
+            hist2 = hist.clone()
+            x, x2 = dev(x0), dev(x0)
+            h = torch.empty((T, width), dtype=out_dtype, device=DEV) if out_dtype else None
+            ops.norm_add_tail(dev(y), dev(g1), eps, x, mix=(hist, n_terms, dev(w)) if with_mix else None,
+                              then=(dev(g2), eps, "layer", h) if h is not None else None)
+            want_x = mixed if with_mix else summed
+            assert np.abs(x.cpu().numpy() - want_x).max() < 1e-5
+            ops.norm_rows(dev(y), dev(g1), None, eps, x2, add=True)
+            if with_mix:
+                ops.depth_mix(x2, hist2, n_terms, dev(w))
+                assert torch.equal(hist, hist2)
+            assert torch.equal(x, x2)
+            if h is not None:
+                h2 = torch.empty_like(h)
+                ops.norm_rows(x2, dev(g2), None, eps, h2)
+                assert torch.equal(h, h2)
+                assert np.abs(h.float().cpu().numpy() - P.layer_norm(want_x, g2, eps)).max() < (1e-5 if out_dtype == torch.float32 else 0.06)
+
+
 def _scan_inputs(rng, n, W, gate_shift):
     """Projection weights that are identities, so that the plain function's gate, candidate and
     output-gate inputs are the rows themselves (plus a bias)."""
@@ -185,6 +220,10 @@ def test_attention_over_shared_rows_far_keys_and_page_borders(dtype, rank, heads
         elif kernel == "decode":
             ops.attention_decode_shared(dev(q, dtype), cache, bt, i32([0] * T), i32(positions), out, heads, 1.0, None,
                                         max(positions) + 1)
+        elif kernel.startswith("latent"):           # all heads a block; key ranges: as chosen, one, three, sixteen
+            ops.attention_latent_decode(dev(q, dtype), cache, bt, i32([0] * T), i32(positions), out, heads, 1.0, None,
+                                        max(positions) + 1, n_splits={"latent": None, "latent1": 1, "latent3": 3,
+                                                                      "latent16": 16}[kernel])
         else:
             ops.attention_prefill_tc(dev(q, dtype), cache, bt, i32([0, T]), i32([positions[-1] + 1]), out, heads, 1.0,
                                      None, 1, T, kv_shared=True)
@@ -192,7 +231,8 @@ def test_attention_over_shared_rows_far_keys_and_page_borders(dtype, rank, heads
 
     kernels = ["general"]
     if dtype == torch.bfloat16 and rank % 8 == 0:
-        kernels.append("decode")
+        kernels += ["decode", "latent", "latent1", "latent3", "latent16"]
+        assert ops.attention_latent_decode_supported(dev(np.zeros((1, heads * rank)), dtype), cache, heads)
     portion_kernels = ["general"] + (["tensor"] if dtype == torch.bfloat16 and rank in (64, 128) else [])
     # random queries: a portion of the last 70 positions, a portion that starts at 0, and single tokens
     q = rng.standard_normal((n, heads * rank)) * 1.5
