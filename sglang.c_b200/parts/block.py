@@ -38,6 +38,8 @@ class SandwichNormBlock(Part):
     sums it into the 32-bit stream in the same kernel.  A layer with a `depth_mix` sub-part
     (category stream_mix) hands x to it before and after."""
 
+    MIX_IN_TAIL_MAX_ROWS = 256
+
     def workspace_per_token(self, layer):
         act = 4 if self.rt.dtype == "float32" else 2
         E = layer.norm1.params["size"]
@@ -61,8 +63,10 @@ class SandwichNormBlock(Part):
         ctx.release(inner)
         # the norm behind a sublayer takes the next step along in its launch: the norm ahead of the
         # feed-forward, or (behind the layer's last sublayer) the depth mix
+        # (the mix joins that launch in steps of few rows, where a launch costs more than its bytes;
+        # over many rows the mix's own kernel streams the kept results several times faster)
         has_ffn = "ffn" in layer.parts
-        terms = mix.terms(ctx) if mix is not None else None
+        terms = mix.terms(ctx) if mix is not None and T <= self.MIX_IN_TAIL_MAX_ROWS else None
         done = layer.norm1b.add_into(ctx, y, x, then=(layer.norm2, h) if has_ffn else None,
                                      mix=None if has_ffn else terms)
         if has_ffn:

@@ -427,3 +427,24 @@ def test_greedy_generation_through_the_scheduler(dirs, name, dtype):
         check_greedy(d, p, g, 1e-4 if dtype == "float32" else 5e-2)
     st = s.get_stats()
     assert st.n_finished == len(prompts) and st.pool_free == st.pool_pages
+
+
+def test_command_line_generates_from_a_random_folder(tmp_path):
+    """bin/sglc: a random folder written from a config.json, then greedy generation from it."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(TUK["C"]))
+    d = str(tmp_path / "model")
+    prompt = [5, 17, 3, 99, 42]
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "sglc"), "--random-weights", "11", "--config", str(cfg),
+                           "--init", "varied", "--save-model", d, "--dtype", "float32", "--prompt",
+                           " ".join(map(str, prompt)), "--max-new", "8", "--temperature", "0", "--page-size", "8"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    ids = [int(t) for t in proc.stdout.strip().splitlines()[-1].split()]
+    assert ids[:len(prompt)] == prompt and len(ids) == len(prompt) + 8
+    check_greedy(d, prompt, ids[len(prompt):], 1e-4)
