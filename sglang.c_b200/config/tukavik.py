@@ -9,7 +9,8 @@ feed-forward.  Every size and every constant that may differ between models come
                  "mlp": {"kind": "dense", "ff": F}},
                 {"type": "latent_attention_2", "mixer": {... , "q_rank", optional "kv_from": j}, "mlp": ...}]}
 
-`kv_from: j` makes a layer read the latents layer j caches instead of projecting its own.
+`kv_from: j` makes an attention layer (of either kind) read the latents layer j caches instead of
+projecting its own.
 An optional `max_positions` bounds a request's length (positions are computed, not looked up,
 so the architecture itself has no bound).
 """
@@ -86,13 +87,13 @@ class TukavikConfig:
                     layers.append(TukavikLayer(kind, width=get_int(m, "width", minimum=1), ff=ff))
                     continue
                 kv_from = get_int(m, "kv_from", default=None, minimum=0)
-                if kv_from is not None and kind != "latent_attention_2":
-                    raise ConfigError("config.json: key 'kv_from' belongs to latent_attention_2 layers")
+                dim = get_int(m, "dim", minimum=1)
                 layer = TukavikLayer(
-                    kind, heads=get_int(m, "heads", minimum=1), dim=get_int(m, "dim", minimum=1),
+                    kind, heads=get_int(m, "heads", minimum=1), dim=dim,
                     vdim=get_int(m, "vdim", minimum=1), kv_rank=get_int(m, "kv_rank", minimum=1),
                     q_rank=get_int(m, "q_rank", minimum=1) if kind == "latent_attention_2" else None,
-                    scale=get_float(m, "scale", positive=True), kv_from=kv_from, ff=ff)
+                    # (a file that leaves the multiplier out means the usual 1/sqrt(dim))
+                    scale=get_float(m, "scale", default=dim ** -0.5, positive=True), kv_from=kv_from, ff=ff)
             except ConfigError as e:
                 raise ConfigError(f"{e} (in {where}.mixer)") from None
             if kv_from is not None:
