@@ -147,15 +147,24 @@ __device__ __forceinline__ float xielu_fast(float u, float ap, float an) {
   return u > 0.0f ? fmaf(ap * u, u, 0.5f * u) : fmaf(an, (e - 1.0f) - u, 0.5f * u);
 }
 __device__ __forceinline__ float act_tc(float u, int act) {
-  if (act == SGLC_ACT_NONE) return u;
   if (act == SGLC_ACT_GELU_TANH) return gelu_tanh_sigmoid(u);
   if (act == SGLC_ACT_GELU_ERF) return gelu_erf_f32(u);
-  if ((act & 0xff) == SGLC_ACT_XIELU) {
-    const float2 p = c_sglc_act_params[(act >> 8) & 0xff];
-    return xielu_fast(u, p.x, p.y);
-  }
   return u;
 }
+// The tensor-core products exist twice: XI = false with the epilogue above, as it always was, and
+// XI = true for xIELU alone.  (One epilogue that chose among all kinds at run time made every
+// product of a decode step 0.35 us slower, whatever its activation: the unrolled epilogue loops
+// were laid out once per kind.)
+template <bool XI>
+__device__ __forceinline__ float act_tc_k(float u, int act) {
+  if constexpr (XI) {
+    const float2 p = c_sglc_act_params[(act >> 8) & 0xff];
+    return xielu_fast(u, p.x, p.y);
+  } else {
+    return act_tc(u, act);
+  }
+}
+__host__ __device__ __forceinline__ bool act_is_xielu(int act) { return (act & 0xff) == SGLC_ACT_XIELU; }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -68,6 +68,7 @@ __device__ __forceinline__ uint4 load16_tokens(const uint4* p, bool on) {
   return v;
 }
 
+template <bool XI>
 __global__ void __launch_bounds__(MAX_WARPS * 32) gemm_few_kernel(const FewArgs a) {
   __shared__ float red[MAX_WARPS][32][2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -121,8 +122,8 @@ __global__ void __launch_bounds__(MAX_WARPS * 32) gemm_few_kernel(const FewArgs 
     const float v = vals[e] + (a.bias ? a.bias[f] : 0.0f);
     const size_t at = (size_t)m * a.ldo + f;
     if (a.residual) a.residual[at] += v;
-    else if (a.out_f32) reinterpret_cast<float*>(a.out)[at] = act_tc(v, a.act);
-    else reinterpret_cast<__nv_bfloat16*>(a.out)[at] = __float2bfloat16_rn(act_tc(v, a.act));
+    else if (a.out_f32) reinterpret_cast<float*>(a.out)[at] = act_tc_k<XI>(v, a.act);
+    else reinterpret_cast<__nv_bfloat16*>(a.out)[at] = __float2bfloat16_rn(act_tc_k<XI>(v, a.act));
   }
 }
 
@@ -149,5 +150,7 @@ SGLC_API int sglc_gemm_few(const void* A, const void* W, const float* bias, void
   const int n_groups = (K / 8 + 3) / 4;
   int warps = (n_groups + 3) / 4;                    // about four groups a warp (measured against 3 and 6)
   warps = warps < 4 ? 4 : (warps > MAX_WARPS ? MAX_WARPS : warps);
-  return sglc_launch(gemm_few_kernel, dim3((N + FB - 1) / FB), dim3(warps * 32), 0, stream, 1, true, a);
+  if (act_is_xielu(act))
+    return sglc_launch(gemm_few_kernel<true>, dim3((N + FB - 1) / FB), dim3(warps * 32), 0, stream, 1, true, a);
+  return sglc_launch(gemm_few_kernel<false>, dim3((N + FB - 1) / FB), dim3(warps * 32), 0, stream, 1, true, a);
 }

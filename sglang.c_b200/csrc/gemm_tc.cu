@@ -86,7 +86,7 @@ struct SharedCtl {
   int abort_flag;
 };
 
-template <int BN>
+template <int BN, bool XI>
 __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, int q0, const float* v,
                                                int nq) {
   // v[j]: value at (p_glob, q0 + j), already reduced over K; applies bias, activation, store.
@@ -98,7 +98,7 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, in
     for (int j = 0; j < nq; j++) {
       int m = q0 + j;
       if (m >= a.M) break;
-      float x = act_tc(v[j] + b, a.act);
+      float x = act_tc_k<XI>(v[j] + b, a.act);
       size_t o = (size_t)m * a.ldo + n;
       if (a.residual) a.residual[o] += x;
       else if (a.out_f32) ((float*)a.out)[o] = x;
@@ -128,7 +128,7 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, in
     } else if (a.out_f32) {
       float* dst = (float*)a.out + row + q0;
       for (int j = 0; j < nq && q0 + j < a.N; j++)
-        dst[j] = act_tc(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act);
+        dst[j] = act_tc_k<XI>(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act);
     } else {
       __nv_bfloat16* dst = (__nv_bfloat16*)a.out + row + q0;
       if (vec_ok && ((uintptr_t)dst & 15) == 0 && nq % 8 == 0) {
@@ -137,22 +137,22 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, in
           __align__(16) __nv_bfloat162 h[4];
 #pragma unroll
           for (int t = 0; t < 4; t++) {
-            float x0 = act_tc(v[j + 2 * t] + (a.bias ? a.bias[q0 + j + 2 * t] : 0.0f), a.act);
+            float x0 = act_tc_k<XI>(v[j + 2 * t] + (a.bias ? a.bias[q0 + j + 2 * t] : 0.0f), a.act);
             float x1 =
-                act_tc(v[j + 2 * t + 1] + (a.bias ? a.bias[q0 + j + 2 * t + 1] : 0.0f), a.act);
+                act_tc_k<XI>(v[j + 2 * t + 1] + (a.bias ? a.bias[q0 + j + 2 * t + 1] : 0.0f), a.act);
             h[t] = __floats2bfloat162_rn(x0, x1);
           }
           *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<uint4*>(h);
         }
       } else {
         for (int j = 0; j < nq && q0 + j < a.N; j++)
-          dst[j] = __float2bfloat16_rn(act_tc(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act));
+          dst[j] = __float2bfloat16_rn(act_tc_k<XI>(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act));
       }
     }
   }
 }
 
-template <int BN>
+template <int BN, bool XI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                const __grid_constant__ CUtensorMap map_out, const GemmArgs a) {
@@ -313,7 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           tmem_ld_wait();
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + s_bias[c + j], a.act);
+          for (int j = 0; j < 32; j++) v[j] = act_tc_k<XI>(__uint_as_float(r[j]) + s_bias[c + j], a.act);
           if (to_f32) {
             // box = 32 floats (128 bytes) per row: this chunk is row `row` of box c/32
             uint8_t* box = smem + (size_t)(c / 32) * (BM * 128);
@@ -373,7 +373,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < CH; j++) v[j] = 0.0f;
         }
-        epilogue_store<BN>(a, p_glob, qt * BN + c, v, CH);
+        epilogue_store<BN, XI>(a, p_glob, qt * BN + c, v, CH);
       }
     } else if (ok) {
       // split-K: the tile's 128 rows are dealt out to the cluster's blocks; every block sends
@@ -436,7 +436,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
           for (int u = 0; u < 4; u++) {
             if (!valid[u]) continue;
-            float x = act_tc(v[u] + bs[u], a.act);
+            float x = act_tc_k<XI>(v[u] + bs[u], a.act);
             if (a.residual) a.residual[off[u]] = rs[u] + x;
             else if (a.out_f32) ((float*)a.out)[off[u]] = x;
             else ((__nv_bfloat16*)a.out)[off[u]] = __float2bfloat16_rn(x);
@@ -477,7 +477,7 @@ struct StreamCtl {
   int abort_flag;
 };
 
-template <int BN, bool KV>
+template <int BN, bool KV, bool XI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const __grid_constant__ CUtensorMap map_out, const GemmArgs a, const KvArgs kv) {
@@ -643,7 +643,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           }
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + bias_s[c + j], a.act);
+          for (int j = 0; j < 32; j++) v[j] = act_tc_k<XI>(__uint_as_float(r[j]) + bias_s[c + j], a.act);
           if (KV && qt * BN + c >= kv.q_cols) {
             // 32 columns of keys or values (they lie within one head): 64 bytes of this token's
             // row in its page, straight from the registers
@@ -712,7 +712,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-          epilogue_store<BN>(a, p_glob, qt * BN + c, v, 32);
+          epilogue_store<BN, XI>(a, p_glob, qt * BN + c, v, 32);
         }
       }
     }
@@ -738,7 +738,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 // arrival from the even block's commits (the commit's multicast); the even block's acc_empty[b]
 // gets one from each epilogue warp of both blocks.  Otherwise the kernel above: one ring across
 // all of a pair's tiles, two accumulators, the same epilogues.
-template <int BN, bool KV>
+template <int BN, bool KV, bool XI>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const GemmArgs a, const KvArgs kv) {
@@ -918,7 +918,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (c + 32 >= c_lo + GC) release();
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + bias_s[c + j], a.act);
+          for (int j = 0; j < 32; j++) v[j] = act_tc_k<XI>(__uint_as_float(r[j]) + bias_s[c + j], a.act);
           if (KV && qt * BN + c >= kv.q_cols) {
             // 32 columns of keys or values (within one head): 64 bytes of this token's row in its page
             if (!live || qt * BN + c >= a.N) continue;
@@ -1029,7 +1029,7 @@ bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, u
   return true;
 }
 
-template <int BN>
+template <int BN, bool XI>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mo, const GemmArgs& a,
            dim3 grid, cudaStream_t stream) {
   size_t smem = (size_t)a.stages * (BM * BK * 2 + BN * BK * 2);
@@ -1037,12 +1037,12 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mo, 
   smem += 1024;
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, XI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     // ask for the largest shared-memory split of the SM, so that two blocks fit side by side
     // (one block's epilogue then overlaps the other's main loop)
-    cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(gemm_tc_kernel<BN, XI>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
     configured = smem;
   }
@@ -1051,9 +1051,9 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mo, 
     size_t need = (size_t)((a.residual || a.out_f32) ? BN / 32 : BN / 64) * BM * 128 + 1024;
     if (smem < need) smem = need;
   }
-  return sglc_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, mo, a);
+  return sglc_launch(gemm_tc_kernel<BN, XI>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, mo, a);
 }
-template <int BN, bool KV>
+template <int BN, bool KV, bool XI>
 int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a, const KvArgs& kv,
                   cudaStream_t stream) {
   static int n_sm = 0;
@@ -1070,7 +1070,7 @@ int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMa
   if (granted == 0) {
     for (; stages >= 2; stages--) {
       const size_t want = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
-      if (cudaFuncSetAttribute(gemm_tc_stream_kernel<BN, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
+      if (cudaFuncSetAttribute(gemm_tc_stream_kernel<BN, KV, XI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
           cudaSuccess)
         break;
       cudaGetLastError();
@@ -1082,12 +1082,12 @@ int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMa
   a.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
   int grid = a.n_tiles < n_sm ? a.n_tiles : n_sm;
-  return sglc_launch(gemm_tc_stream_kernel<BN, KV>, dim3(grid), dim3(THREADS), smem, stream, 1, true, ma, mw, mo, a, kv);
+  return sglc_launch(gemm_tc_stream_kernel<BN, KV, XI>, dim3(grid), dim3(THREADS), smem, stream, 1, true, ma, mw, mo, a, kv);
 }
 // The two-SM kernel: clusters of two blocks, as many as the device holds at once (148 SMs: 74;
 // what the first launch learns from the occupancy query replaces the guess).
 int g_pairs_at_once = 74;
-template <int BN, bool KV>
+template <int BN, bool KV, bool XI>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a, const KvArgs& kv,
                 cudaStream_t stream) {
   const size_t stage_bytes = (size_t)BM * BK * 2 + (size_t)(BN / 2) * BK * 2;
@@ -1097,7 +1097,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     for (; stages >= 2; stages--) {
       const size_t want = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
-      if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
+      if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, KV, XI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
           cudaSuccess)
         break;
       cudaGetLastError();
@@ -1115,7 +1115,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
     probe.attrs = pa;
     probe.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN, KV>, &probe) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN, KV, XI>, &probe) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       return SGLC_ERR_UNSUPPORTED;
     }
@@ -1142,7 +1142,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
   }
   cfg.attrs = attr;
   cfg.numAttrs = n;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, KV>, ma, mw, mo, a, kv);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, KV, XI>, ma, mw, mo, a, kv);
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
@@ -1228,6 +1228,7 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
     return SGLC_ERR_UNSUPPORTED;
   int swap, bn, splits, per, tp, tq;
   plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
+  const bool xi = act_is_xielu(act);          // the epilogue's other instantiation
   GemmArgs a;
   a.M = M; a.N = N; a.K = K;
   a.swap = swap;
@@ -1268,8 +1269,9 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
       a.tiles_p = rows2;
       a.n_tiles = t256;
       const KvArgs none = {};
-      const int code = kv ? launch_pair<256, true>(mp, mq, mo, a, *kv, stream)
-                          : launch_pair<256, false>(mp, mq, mo, a, none, stream);
+      const int code = kv ? launch_pair<256, true, false>(mp, mq, mo, a, *kv, stream)
+                          : xi ? launch_pair<256, false, true>(mp, mq, mo, a, none, stream)
+                               : launch_pair<256, false, false>(mp, mq, mo, a, none, stream);
       if (code != SGLC_ERR_UNSUPPORTED) return code;
     }
   }
@@ -1277,8 +1279,9 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
     a.tiles_p = tp;
     a.n_tiles = tp * tq;
     const KvArgs none = {};
-    if (kv) return bn == 128 ? launch_stream<128, true>(mp, mq, mo, a, *kv, stream) : launch_stream<64, true>(mp, mq, mo, a, *kv, stream);
-    return bn == 128 ? launch_stream<128, false>(mp, mq, mo, a, none, stream) : launch_stream<64, false>(mp, mq, mo, a, none, stream);
+    if (kv) return bn == 128 ? launch_stream<128, true, false>(mp, mq, mo, a, *kv, stream) : launch_stream<64, true, false>(mp, mq, mo, a, *kv, stream);
+    if (xi) return bn == 128 ? launch_stream<128, false, true>(mp, mq, mo, a, none, stream) : launch_stream<64, false, true>(mp, mq, mo, a, none, stream);
+    return bn == 128 ? launch_stream<128, false, false>(mp, mq, mo, a, none, stream) : launch_stream<64, false, false>(mp, mq, mo, a, none, stream);
   }
   int stage_bytes = BM * BK * 2 + bn * BK * 2;
   int budget = swap ? 96 * 1024 : (bn == 128 ? 100 * 1024 : 100 * 1024);
@@ -1298,10 +1301,10 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
   a.stages = stages;
   dim3 grid(tp, tq, splits);
   switch (bn) {
-    case 16: return launch<16>(mp, mq, mo, a, grid, stream);
-    case 32: return launch<32>(mp, mq, mo, a, grid, stream);
-    case 64: return launch<64>(mp, mq, mo, a, grid, stream);
-    case 128: return launch<128>(mp, mq, mo, a, grid, stream);
+    case 16: return xi ? launch<16, true>(mp, mq, mo, a, grid, stream) : launch<16, false>(mp, mq, mo, a, grid, stream);
+    case 32: return xi ? launch<32, true>(mp, mq, mo, a, grid, stream) : launch<32, false>(mp, mq, mo, a, grid, stream);
+    case 64: return xi ? launch<64, true>(mp, mq, mo, a, grid, stream) : launch<64, false>(mp, mq, mo, a, grid, stream);
+    case 128: return xi ? launch<128, true>(mp, mq, mo, a, grid, stream) : launch<128, false>(mp, mq, mo, a, grid, stream);
   }
   return SGLC_ERR_ARGUMENT;
 }
