@@ -146,15 +146,15 @@ def _scan_inputs(rng, n, W, gate_shift):
     return h, eye, bz, bx
 
 
+@pytest.mark.parametrize("W", [150, 160])          # one channel a thread; four (16-byte loads)
 @pytest.mark.parametrize("gate_shift", [0.0, -4.0])
-def test_mingru_scan_short_and_chunked_with_carried_state(gate_shift):
+def test_mingru_scan_short_and_chunked_with_carried_state(gate_shift, W):
     """Requests of unequal lengths in one step (single tokens beside portions longer than a chunk,
     chunk edges at 127/128/129), then the same sequences continued in a second step from the
     state the first left, with the slots in another order.  gate_shift -4 makes the gate open to
     about 2 %: the state then remembers hundreds of tokens, and one reset would show."""
     from sglang_c_b200.csrc import ops
     rng = np.random.default_rng(11)
-    W = 150
     for first, second in (([1, 5, 128, 64], [1, 1, 1, 1]),               # the one-launch way, then decoding
                           ([127, 1, 300, 129], [2, 256, 129, 1]),        # the chunked way both times
                           ([128, 385], [3, 2])):
