@@ -820,7 +820,7 @@ def main():
                     help="also medium and XL layer sizes (decode at batch 8, prefill) and the mixed workload "
                          "(64 requests, prompts of 16..1024 tokens, 128 generated each) under `points`")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
-                    help="decode: the contract's line; mixed: only the mixed workload through the scheduler")
+                    help="decode: the default line; mixed: only the mixed workload through the scheduler")
     ap.add_argument("--batch", type=int, default=BATCH, help="with --only decode: requests decoding together")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "fp32"],
                     help="a handful of steps of one kind and nothing else (what a profiler is pointed at): "

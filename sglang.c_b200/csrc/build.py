@@ -33,7 +33,7 @@ def set_bounds_check(on):
     """From now on load the bounds-check build of every kernel library (compiled with
     -DSGLC_BOUNDS_CHECK into files of their own): indices that kernels take from device memory
     are compared with their ranges before use, see common.cuh.  For tests and for hunting a bad
-    index where no memory checker can be run; the ordinary build is what serves."""
+    index where no memory-checking tool can be run; the ordinary build is what serves."""
     global _bounds_check
     with _lock:
         _bounds_check = bool(on)

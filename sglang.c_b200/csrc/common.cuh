@@ -67,7 +67,7 @@ static inline int sglc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 // The bounds-check build (-DSGLC_BOUNDS_CHECK, see build.set_bounds_check): every index that a
 // kernel takes from device memory (a page id out of a block table, a cache slot, a row number) is
 // compared with its range before it is used; an index outside is not dereferenced: the access is
-// skipped and the error word gets SGLC_FLAG_INDEX.  (The stand-in for a memory checker where none
+// skipped and the error word gets SGLC_FLAG_INDEX.  (The stand-in for a memory-checking tool where none
 // can be run; the ordinary build trusts what the host validated when it built the step.)
 enum { SGLC_FLAG_WAIT = 1, SGLC_FLAG_INDEX = 4 };
 #ifdef SGLC_BOUNDS_CHECK
