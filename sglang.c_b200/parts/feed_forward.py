@@ -34,9 +34,10 @@ class MLP(Part):
         self.act_params = self.act_slot = None
         if self.params["activation"] == "xielu":
             from ..csrc import ops
-            pq = tensors["act_params"].tensor.double()
-            sp = torch.nn.functional.softplus(pq)
-            self.act_params = (float(sp[0]), 0.5 + float(sp[1]))
+            import math
+            p, q = (float(v) for v in tensors["act_params"].tensor.double().tolist())
+            softplus = lambda v: max(v, 0.0) + math.log1p(math.exp(-abs(v)))
+            self.act_params = (softplus(p), 0.5 + softplus(q))
             if self.rt is not None:
                 libs = ["gemm_simt"] + (["gemm_tc", "gemm_few"] if self.rt.dtype == "bfloat16" else [])
                 self.act_slot = ops.register_act_params(*self.act_params, libs)
