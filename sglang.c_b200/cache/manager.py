@@ -31,6 +31,7 @@ class _Group:
 class CacheManager:
     """needs[i] is the CacheNeed (or None) of the i-th call of the running
     order; cache_of[i] names the earlier call whose cache call i reads.
+    A need may be a tuple of needs; the call's binding is then a tuple of bindings.
     `make_tensor(shape, dtype_name)` allocates device memory (None in host-only
     tests)."""
 
@@ -45,22 +46,34 @@ class CacheManager:
         self._call_group = {}          # owning call -> (group index, index within the group)
         self._bindings = {}
         by_need = {}
-        for i, need in enumerate(needs):
-            if need is None or cache_of[i] is not None:
+        # a call's need may be a tuple of needs (a mixer that keeps several things): every one of them
+        # is placed by itself, under the key (call, index within the tuple)
+        def subs(i):
+            need = needs[i]
+            if need is None:
+                return []
+            return list(enumerate(need)) if isinstance(need, (tuple, list)) else [(None, need)]
+        for i in range(len(needs)):
+            if cache_of[i] is not None:
                 continue
-            gi = by_need.get(need)
-            if gi is None:
-                gi = len(self.groups)
-                by_need[need] = gi
-                self.groups.append(_Group(need, []))
-            g = self.groups[gi]
-            self._call_group[i] = (gi, len(g.calls))
-            g.calls.append(i)
+            for j, need in subs(i):
+                gi = by_need.get(need)
+                if gi is None:
+                    gi = len(self.groups)
+                    by_need[need] = gi
+                    self.groups.append(_Group(need, []))
+                g = self.groups[gi]
+                self._call_group[(i, j)] = (gi, len(g.calls))
+                g.calls.append(i)
         for g in self.groups:
             if g.need.kind == "paged_kv":
                 g.pool = PagePool(self.n_pages)
-                shape = (len(g.calls), self.n_pages, 1 if g.need.shared else 2, g.need.n_kv_heads, self.page_size,
-                         g.need.head_dim)
+                if g.need.v_dim is not None:
+                    shape = (len(g.calls), self.n_pages,
+                             g.need.n_kv_heads * self.page_size * (g.need.head_dim + g.need.v_dim))
+                else:
+                    shape = (len(g.calls), self.n_pages, 1 if g.need.shared else 2, g.need.n_kv_heads, self.page_size,
+                             g.need.head_dim)
                 dt = cache_dtype
             elif g.need.kind == "state":
                 shape = (len(g.calls), self.max_requests) + tuple(g.need.state_shape)
@@ -68,18 +81,20 @@ class CacheManager:
             else:
                 raise CacheError(f"unknown cache need kind '{g.need.kind}'")
             g.tensor = make_tensor(shape, dt) if make_tensor is not None else None
-        for i, need in enumerate(needs):
-            if need is None:
+        for i in range(len(needs)):
+            if needs[i] is None:
                 continue
             owner = i if cache_of[i] is None else cache_of[i]
-            if owner not in self._call_group:
-                raise CacheError(f"call {i} reads the cache of call {owner}, which keeps none")
-            if needs[owner] != need:
+            if needs[owner] != needs[i]:
                 raise CacheError(f"call {i} reads the cache of call {owner} but their needs differ")
-            gi, ci = self._call_group[owner]
-            t = self.groups[gi].tensor
-            self._bindings[i] = CacheBinding(need.kind, gi, t[ci] if t is not None else None,
-                                             write=(owner == i))
+            made = []
+            for j, need in subs(i):
+                if (owner, j) not in self._call_group:
+                    raise CacheError(f"call {i} reads the cache of call {owner}, which keeps none")
+                gi, ci = self._call_group[(owner, j)]
+                t = self.groups[gi].tensor
+                made.append(CacheBinding(need.kind, gi, t[ci] if t is not None else None, write=(owner == i)))
+            self._bindings[i] = tuple(made) if isinstance(needs[i], (tuple, list)) else made[0]
         # per-request bookkeeping
         self._free_slots = list(range(self.max_requests - 1, -1, -1))
         self._slot = {}
@@ -123,9 +138,11 @@ class CacheManager:
 
     def _first_needed_block(self, g, length):
         """First block a query at position >= `length` can still see."""
-        if g.need.window is None:
-            return 0
-        first_pos = max(0, length - g.need.window + 1)
+        first_pos = 0
+        if g.need.window is not None:
+            first_pos = max(0, length - g.need.window + 1)
+        if g.need.chunk is not None:
+            first_pos = max(first_pos, length // g.need.chunk * g.need.chunk)
         return first_pos // self.page_size
 
     def pages_needed(self, req, new_len):

@@ -1,9 +1,10 @@
 from .base import ConfigError, read_config_json
 from .gpt2 import GPT2Config
 from .tukavik import TukavikConfig, TukavikLayer
+from .zuretar import ZuretarConfig, ZuretarLayer
 from .registry import (Architecture, known_architectures, load_config,
                        register_architecture, resolve_architecture)
 
-__all__ = ["ConfigError", "read_config_json", "GPT2Config", "TukavikConfig", "TukavikLayer", "Architecture",
+__all__ = ["ConfigError", "read_config_json", "GPT2Config", "TukavikConfig", "TukavikLayer", "ZuretarConfig", "ZuretarLayer", "Architecture",
            "known_architectures", "load_config", "register_architecture",
            "resolve_architecture"]

@@ -30,13 +30,19 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
 }
 
 // W: tokens of a block (a warp each).  Threads beyond the tokens' warps only help to stage tiles.
-template <typename TQ, typename TC, typename TO, int W, int THREADS>
+// EXT: the form with a value size DV of its own (a page then holds Hkv x page_size x D keys
+// followed by Hkv x page_size x DV values), a chunk mask (a query sees only keys of its own chunk of
+// `chunk` positions, counted from position 0) and a sink per head (a learned score that joins the
+// softmax's denominator once, with no key and no value).  Without EXT the three arguments are unused.
+template <typename TQ, typename TC, typename TO, int W, int THREADS, bool EXT>
 __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 3 : 4)     // (registers capped so that three blocks of 256 share an SM)
 attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restrict__ cache,
                       const int* __restrict__ block_table, int bt_stride,
                       const int* __restrict__ token_req, const int* __restrict__ positions,
                       TO* __restrict__ out, int o_stride, int T, int H, int Hkv, int D, int page_size,
-                      float scale, int window, int n_pages, int* err, int kv_shared) {
+                      float scale, int window, int n_pages, int* err, int kv_shared,
+                      int DV_arg, int chunk, const float* __restrict__ sinks) {
+  const int DV = EXT ? DV_arg : D;
   extern __shared__ __align__(16) float smem[];
   __shared__ int s_req[W], s_lo[W], s_pos[W];
   // padded key rows: a lane a key without bank conflicts (by 4 where rows are read 16 bytes at a time)
@@ -44,7 +50,7 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
   const int DP = wide ? D + 4 : D + 1;
   float* Ks = smem;                           // [32][DP]
   float* Vs = Ks + 32 * DP;                   // [32][D]
-  float* pw = Vs + 32 * D;                    // [W][32]: a tile's weights (16-byte aligned whatever D is)
+  float* pw = Vs + 32 * DV;                   // [W][32]: a tile's weights (16-byte aligned whatever D is)
   float* qs = pw + W * 32;                    // [W][D]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y, hk = h / (H / Hkv);
@@ -55,7 +61,9 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
     const int pos = on ? positions[t] : -1;
     s_req[tid] = on ? token_req[t] : -1;
     s_pos[tid] = pos;
-    s_lo[tid] = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (EXT && chunk > 0 && pos >= 0) lo = max(lo, pos / chunk * chunk);
+    s_lo[tid] = lo;
   }
   if (warp < W && t0 + warp < T) {
     const TQ* qp = q + (size_t)(t0 + warp) * q_stride + (size_t)h * D;
@@ -69,7 +77,7 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
 #pragma unroll
   for (int i = 0; i < 8; i++) acc[i] = 0.0f;
   // kv_shared: a page holds one block of rows that are keys and values at once (a latent)
-  const size_t page_elems = (size_t)(kv_shared ? 1 : 2) * Hkv * page_size * D;
+  const size_t page_elems = EXT ? (size_t)Hkv * page_size * (D + DV) : (size_t)(kv_shared ? 1 : 2) * Hkv * page_size * D;
   const size_t head_off = (size_t)hk * page_size * D, v_off = kv_shared ? 0 : (size_t)Hkv * page_size * D;
 
   // The tokens of a block that belong to one request (a run: a request's tokens lie together)
@@ -97,7 +105,13 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
           if (sglc_index_ok(page, n_pages, err))
             kp = cache + (size_t)page * page_elems + head_off + (size_t)(p % page_size) * D;
         }
-        if (D % 4 == 0) {
+        if (EXT) {
+          const TC* vp = kp ? cache + (size_t)(bt[p / page_size]) * page_elems + (size_t)Hkv * page_size * D +
+                                  ((size_t)hk * page_size + p % page_size) * DV
+                            : nullptr;
+          for (int d = part; d < D; d += TPK) Ks[j * DP + d] = kp ? to_f32(kp[d]) : 0.0f;
+          for (int d = part; d < DV; d += TPK) Vs[j * DV + d] = vp ? to_f32(vp[d]) : 0.0f;
+        } else if (D % 4 == 0) {
           for (int d = part * 4; d < D; d += 4 * TPK) {
             float k4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, v4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (kp) {
@@ -151,10 +165,10 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const int d = lane + 32 * i;
-          if (d < D) {
+          if (d < DV) {
             float a = acc[i] * corr;
 #pragma unroll
-            for (int j = 0; j < 32; j++) a = fmaf(pj[j], Vs[j * D + d], a);
+            for (int j = 0; j < 32; j++) a = fmaf(pj[j], Vs[j * DV + d], a);
             acc[i] = a;
           }
         }
@@ -163,12 +177,16 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
     }
   }
   if (mine) {
-    TO* op = out + (size_t)(t0 + warp) * o_stride + (size_t)h * D;
-    const float inv = 1.0f / l;
+    TO* op = out + (size_t)(t0 + warp) * o_stride + (size_t)h * DV;
+    float inv = 1.0f / l;
+    if (EXT && sinks) {                        // the sink joins the denominator: exp(sink - max) once
+      const float sk = sinks[h], m_all = fmaxf(m, sk);
+      inv = expf(m - m_all) / (l * expf(m - m_all) + expf(sk - m_all));
+    }
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const int d = lane + 32 * i;
-      if (d < D) op[d] = from_f32<TO>(acc[i] * inv);
+      if (d < DV) op[d] = from_f32<TO>(acc[i] * inv);
     }
   }
 }
@@ -185,24 +203,33 @@ static int attention_simt_run(const void* q, int q_stride, const void* cache,
                               const int* positions, void* out, int o_stride, int T, int H,
                               int Hkv, int D, int page_size, float scale, int window,
                               int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
-                              int max_q_len, int kv_shared, cudaStream_t stream) {
+                              int max_q_len, int kv_shared, cudaStream_t stream, bool ext = false, int DV = 0,
+                              int chunk = 0, const float* sinks = nullptr) {
   if (T <= 0) return SGLC_OK;
+  if (!ext) DV = D;
+  if (DV <= 0 || DV > 256 || chunk < 0) return ext ? SGLC_ERR_UNSUPPORTED : SGLC_ERR_ARGUMENT;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || page_size <= 0 || max_keys <= 0)
     return SGLC_ERR_ARGUMENT;
   if (H > 65535 || D > 256) return SGLC_ERR_UNSUPPORTED;
   // single tokens of many requests share nothing: a token a block; portions: eight tokens a block
   const bool single = max_q_len <= 1;
   const int W = single ? 1 : 8;
-  const size_t smem = ((size_t)32 * (D % 4 == 0 ? D + 4 : D + 1) + (size_t)32 * D + (size_t)W * D + (size_t)W * 32) * sizeof(float);
+  const size_t smem = ((size_t)32 * (D % 4 == 0 ? D + 4 : D + 1) + (size_t)32 * DV + (size_t)W * D + (size_t)W * 32) * sizeof(float);
   dim3 grid((T + W - 1) / W, H);
-#define LAUNCH(TQ, TC, TO, WW, TH)                                                                     \
+#define LAUNCH_E(TQ, TC, TO, WW, TH, EX)                                                               \
   do {                                                                                                 \
     if (smem > 48 * 1024)                                                                              \
-      cudaFuncSetAttribute(attention_simt_kernel<TQ, TC, TO, WW, TH>,                                  \
+      cudaFuncSetAttribute(attention_simt_kernel<TQ, TC, TO, WW, TH, EX>,                              \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                    \
-    attention_simt_kernel<TQ, TC, TO, WW, TH><<<grid, TH, smem, stream>>>(                              \
+    attention_simt_kernel<TQ, TC, TO, WW, TH, EX><<<grid, TH, smem, stream>>>(                          \
         (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions,        \
-        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err, kv_shared);          \
+        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err, kv_shared, DV,       \
+        chunk, sinks);                                                                                 \
+  } while (0)
+#define LAUNCH(TQ, TC, TO, WW, TH)                                                                     \
+  do {                                                                                                 \
+    if (ext) LAUNCH_E(TQ, TC, TO, WW, TH, true);                                                       \
+    else LAUNCH_E(TQ, TC, TO, WW, TH, false);                                                          \
   } while (0)
   if (act_dtype == SGLC_F32 && cache_dtype == SGLC_F32) {
     if (single) LAUNCH(float, float, float, 1, 128);
@@ -214,6 +241,7 @@ static int attention_simt_run(const void* q, int q_stride, const void* cache,
     return SGLC_ERR_ARGUMENT;
   }
 #undef LAUNCH
+#undef LAUNCH_E
   return sglc_launch_status();
 }
 
@@ -239,4 +267,19 @@ SGLC_API int sglc_attention_simt_shared(const void* q, int q_stride, const void*
   return attention_simt_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride,
                             T, H, Hkv, D, page_size, scale, window, max_keys, act_dtype, cache_dtype,
                             n_pages, err, max_q_len, 1, stream);
+}
+
+// The extended form: values of size DV beside keys of size D (cache [n_pages][Hkv x page_size x D keys |
+// Hkv x page_size x DV values]; out rows hold H heads of DV), `chunk` > 0: a query sees the keys of its
+// own chunk of so many positions only; `sinks` (float [H] or null): a score per head that joins the
+// softmax's denominator.
+SGLC_API int sglc_attention_simt_ext(const void* q, int q_stride, const void* cache,
+                                     const int* block_table, int bt_stride, const int* token_req,
+                                     const int* positions, void* out, int o_stride, int T, int H,
+                                     int Hkv, int D, int DV, int page_size, float scale, int window, int chunk,
+                                     const float* sinks, int max_keys, int act_dtype, int cache_dtype, int n_pages,
+                                     int* err, int max_q_len, cudaStream_t stream) {
+  return attention_simt_run(q, q_stride, cache, block_table, bt_stride, token_req, positions, out, o_stride,
+                            T, H, Hkv, D, page_size, scale, window, max_keys, act_dtype, cache_dtype,
+                            n_pages, err, max_q_len, 0, stream, true, DV, chunk, sinks);
 }

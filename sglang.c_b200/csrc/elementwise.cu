@@ -94,3 +94,46 @@ SGLC_API int sglc_xielu(const void* src, long long src_stride, int src_dtype, vo
 #undef LAUNCH
   return SGLC_ERR_ARGUMENT;
 }
+
+// Gated activation of a feed-forward whose gate and up projections are one product:
+//   dst[r][j] = silu(src[r][j]) * src[r][F + j] * (w ? w[r][j / per] : 1),   j < F
+// src holds the F gate columns, then the F up columns.  With `w` (float [rows][F / per]) a block of
+// `per` columns is one expert of a mixture and takes the token's weight for it (zero: not chosen).
+template <typename TI, typename TO>
+__global__ void gated_act_kernel(const TI* __restrict__ src, long long src_stride, TO* __restrict__ dst,
+                                 long long dst_stride, int rows, int F, const float* __restrict__ w,
+                                 long long w_stride, int per) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)rows * F;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / F;
+    const int c = (int)(i % F);
+    const float wt = w ? w[r * w_stride + c / per] : 1.0f;
+    float out = 0.0f;
+    if (wt != 0.0f) {
+      const float g = to_f32(src[r * src_stride + c]), u = to_f32(src[r * src_stride + F + c]);
+      out = g / (1.0f + expf(-g)) * u * wt;
+    }
+    dst[r * dst_stride + c] = from_f32<TO>(out);
+  }
+}
+
+SGLC_API int sglc_gated_act(const void* src, long long src_stride, int src_dtype, void* dst, long long dst_stride,
+                            int dst_dtype, int rows, int F, const float* w, long long w_stride, int per,
+                            cudaStream_t stream) {
+  if (rows <= 0 || F <= 0) return SGLC_OK;
+  if (w && (per <= 0 || F % per != 0)) return SGLC_ERR_ARGUMENT;
+  const long long total = (long long)rows * F;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+#define LAUNCH(TI, TO)                                                                                  \
+  return sglc_launch(gated_act_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, 1, true, (const TI*)src, \
+                     src_stride, (TO*)dst, dst_stride, rows, F, w, w_stride, per > 0 ? per : 1)
+  if (src_dtype == SGLC_F32 && dst_dtype == SGLC_F32) LAUNCH(float, float);
+  if (src_dtype == SGLC_F32 && dst_dtype == SGLC_BF16) LAUNCH(float, __nv_bfloat16);
+  if (src_dtype == SGLC_BF16 && dst_dtype == SGLC_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+  return SGLC_ERR_ARGUMENT;
+}

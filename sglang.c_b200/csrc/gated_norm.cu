@@ -1,0 +1,54 @@
+// The output stage of a recurrent mixer, for the rows of a step: a row of `width` values (one
+// head's read-out, or all heads' side by side) is divided by its root mean square,
+//   y = o / sqrt(mean(o^2) + eps) * gain * act(gate),
+// with a gain of `width` entries that every row of a token shares and a gate of the row's shape
+// taken through silu or a sigmoid.  Statistics and the gate are 32-bit; the result is written in
+// the precision of the product that follows.  A warp a row.
+#include "common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+enum { GN_SILU = 0, GN_SIGMOID = 1 };
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+gated_norm_kernel(const float* __restrict__ o, long long o_stride, const float* __restrict__ gate,
+                  long long gate_stride, const float* __restrict__ gain, TO* __restrict__ y, long long y_stride,
+                  long long n_rows, int groups, int width, float eps, int act) {
+  pdl_launch_dependents();
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  pdl_wait();
+  if (row >= n_rows) return;
+  const long long t = row / groups;
+  const int c0 = (int)(row % groups) * width;
+  const float* op = o + t * o_stride + c0;
+  const float* gp = gate + t * gate_stride + c0;
+  float ss = 0.0f;
+  for (int d = lane; d < width; d += 32) ss = fmaf(op[d], op[d], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  TO* yp = y + t * y_stride + c0;
+  for (int d = lane; d < width; d += 32) {
+    const float g = gp[d];
+    const float s = 1.0f / (1.0f + expf(-g));
+    yp[d] = from_f32<TO>(op[d] * inv * gain[d] * (act == GN_SILU ? g * s : s));
+  }
+}
+
+// o, gate: float [T][groups*width] (row strides free); gain: float [width]; y: [T][groups*width]
+SGLC_API int sglc_gated_norm(const float* o, long long o_stride, const float* gate, long long gate_stride,
+                             const float* gain, void* y, long long y_stride, int y_dtype, int T, int groups,
+                             int width, float eps, int act, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (groups <= 0 || width <= 0 || (act != GN_SILU && act != GN_SIGMOID)) return SGLC_ERR_ARGUMENT;
+  const long long n_rows = (long long)T * groups;
+  const dim3 grid((unsigned)((n_rows + 3) / 4));
+  if (y_dtype == SGLC_F32)
+    return sglc_launch(gated_norm_kernel<float>, grid, dim3(128), 0, stream, 1, true, o, o_stride, gate, gate_stride,
+                       gain, (float*)y, y_stride, n_rows, groups, width, eps, act);
+  if (y_dtype == SGLC_BF16)
+    return sglc_launch(gated_norm_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, true, o, o_stride, gate,
+                       gate_stride, gain, (__nv_bfloat16*)y, y_stride, n_rows, groups, width, eps, act);
+  return SGLC_ERR_ARGUMENT;
+}

@@ -801,3 +801,208 @@ def set_pdl(on):
     """Turn programmatic dependent launch on or off in every kernel library (on by default)."""
     for name in build.sources():
         build.load(name).sglc_set_pdl(1 if on else 0)
+
+
+# ---------------------------------------------------------------------------
+# recurrent mixers with a matrix state, their input and output stages
+def _f32_rows(t, what, cols=None):
+    if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or (cols is not None and t.shape[1] != cols):
+        raise KernelError(f"{what} must be float32 rows" + (f" of {cols} columns" if cols is not None else ""))
+
+
+def short_conv(x, taps, tail, y, token_req, q_start, state_slots, n_requests, segments, unit_eps=1e-6,
+               gates=None):
+    """Causal convolution over time per channel, silu, and per segment an optional unit-vector
+    scaling of each head row (see short_conv.cu).  x: float32 [T, >= C] (the channels are its
+    first C columns); taps: float32 [C, K]; tail: float32 [n_slots, K-1, C], a request's last
+    K-1 inputs, read and moved on in place; y: float32 [T, C].  segments: (first channel, head
+    rows, row width, unit, scale) each, covering the C channels.  gates = (heads, beta column,
+    a column, A_log, dt_bias, out [T, 2*heads]): beta = sigmoid(x_b) and decay =
+    exp(-exp(A_log) softplus(x_a + dt_bias)) per head, from two more column blocks of x."""
+    _need_cuda(x, taps, tail, y, token_req, q_start, state_slots)
+    T = y.shape[0]
+    C, K = taps.shape
+    _f32_rows(x, "short_conv: x")
+    _f32_rows(y, "short_conv: y", C)
+    if taps.dtype != torch.float32 or not taps.is_contiguous() or x.shape[0] < T or x.shape[1] < C:
+        raise KernelError("short_conv: taps float32 [C, K]; x has at least C columns")
+    if tail.dtype != torch.float32 or not tail.is_contiguous() or tuple(tail.shape[1:]) != (max(K - 1, 0), C):
+        raise KernelError(f"short_conv: the tail is float32 [n_slots, {K - 1}, {C}]")
+    for t, nm in ((token_req, "token_req"), (q_start, "q_start"), (state_slots, "state_slots")):
+        _i32(t, nm)
+    if sum(s[1] * s[2] for s in segments) != C:
+        raise KernelError("short_conv: the segments must cover the channels")
+    segs = (ctypes.c_int * (4 * len(segments)))(*[int(v) for s in segments for v in s[:4]])
+    scales = (ctypes.c_float * len(segments))(*[float(s[4]) for s in segments])
+    if gates is not None:
+        gh, bcol, acol, a_log, dt_bias, gout = gates
+        _need_cuda(a_log, dt_bias, gout)
+        _f32_rows(gout, "short_conv: gates", 2 * gh)
+        if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != gh or dt_bias.numel() != gh \
+                or x.shape[1] < max(bcol, acol) + gh:
+            raise KernelError("short_conv: A_log and dt_bias are float32 [heads]; x holds both gate column blocks")
+    else:
+        gh, bcol, acol, a_log, dt_bias, gout = 0, 0, 0, None, None, None
+    lib = build.load("short_conv")
+    code = lib.sglc_short_conv(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(taps), _ptr(tail), _ptr(y),
+                               ctypes.c_longlong(y.stride(0)), _ptr(token_req), _ptr(q_start), _ptr(state_slots),
+                               T, int(n_requests), C, K, tail.shape[0], ctypes.c_float(unit_eps), segs, scales,
+                               len(segments), gh, int(bcol), int(acol), _ptr(a_log), _ptr(dt_bias), _ptr(gout),
+                               ctypes.c_longlong(gout.stride(0) if gout is not None else 0),
+                               _ptr(tc_error_flag(x.device)), _stream())
+    _check(lib, code, f"short_conv (channels {C}, taps {K})", n_kernels=2 if K > 1 else 1)
+
+
+MATRIX_STATE_MAX_DIM = 256
+
+
+def matrix_state(mode, q, k, v, out, state, q_start, state_slots, n_requests, n_heads, n_qk_heads, dim, v_dim,
+                 gates=None, head_decay=None, silu_in=False):
+    """A recurrence with a matrix state per head over the step's tokens (see matrix_state.cu).
+    mode "decay": S <- d_h S + k v^T (head_decay float32 [H]); mode "delta": the gated delta rule
+    (gates float32 [T, 2H]: beta, then decay).  o = S^T q after the token's write.  q, k: float32
+    [T, n_qk_heads*dim]; v: float32 [T, n_heads*v_dim]; out float32 [T, n_heads*v_dim]; state float32
+    [n_slots, n_heads, dim, v_dim], read and written in place for the requests' slots."""
+    _need_cuda(q, k, v, out, state, q_start, state_slots, gates, head_decay)
+    T = out.shape[0]
+    _f32_rows(q, "matrix_state: q", n_qk_heads * dim)
+    _f32_rows(k, "matrix_state: k", n_qk_heads * dim)
+    _f32_rows(v, "matrix_state: v", n_heads * v_dim)
+    _f32_rows(out, "matrix_state: out", n_heads * v_dim)
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, v_dim):
+        raise KernelError(f"matrix_state: the state is float32 [n_slots, {n_heads}, {dim}, {v_dim}]")
+    if dim > MATRIX_STATE_MAX_DIM:
+        raise KernelError(f"matrix_state: key size {dim} is beyond the kernel's {MATRIX_STATE_MAX_DIM}")
+    _i32(q_start, "q_start")
+    _i32(state_slots, "state_slots")
+    m = {"decay": 0, "delta": 1}[mode]
+    if m == 0 and (head_decay is None or head_decay.dtype != torch.float32 or head_decay.numel() != n_heads):
+        raise KernelError("matrix_state: the decay form takes one float32 decay per head")
+    if m == 1:
+        if gates is None:
+            raise KernelError("matrix_state: the delta rule takes its gates")
+        _f32_rows(gates, "matrix_state: gates", 2 * n_heads)
+    lib = build.load("matrix_state")
+    code = lib.sglc_matrix_state(m, _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), ctypes.c_longlong(k.stride(0)),
+                                 _ptr(v), ctypes.c_longlong(v.stride(0)), _ptr(gates),
+                                 ctypes.c_longlong(gates.stride(0) if gates is not None else 0), _ptr(head_decay),
+                                 _ptr(out), ctypes.c_longlong(out.stride(0)), _ptr(state), state.shape[0],
+                                 _ptr(q_start), _ptr(state_slots), int(n_requests), int(n_heads), int(n_qk_heads),
+                                 int(dim), int(v_dim), 1 if silu_in else 0, _ptr(tc_error_flag(q.device)), _stream())
+    _check(lib, code, f"matrix_state ({mode}, {dim} x {v_dim})")
+
+
+def gated_norm(o, gate, gain, y, groups, width, eps, act):
+    """y = o / sqrt(mean(o^2) + eps) * gain * act(gate) per row of `width` (a token has `groups`
+    rows side by side; gain float32 [width] serves them all); act "silu" or "sigmoid".  o, gate:
+    float32 [T, groups*width]; y: float32 or bfloat16."""
+    _need_cuda(o, gate, gain, y)
+    T = y.shape[0]
+    _f32_rows(o, "gated_norm: o", groups * width)
+    _f32_rows(gate, "gated_norm: gate", groups * width)
+    if gain.dtype != torch.float32 or gain.numel() != width or not gain.is_contiguous():
+        raise KernelError("gated_norm: the gain is a float32 vector of the row width")
+    if tuple(y.shape) != (T, groups * width) or y.stride(1) != 1 or o.shape[0] < T or gate.shape[0] < T:
+        raise KernelError("gated_norm: y is [T, groups*width]")
+    lib = build.load("gated_norm")
+    code = lib.sglc_gated_norm(_ptr(o), ctypes.c_longlong(o.stride(0)), _ptr(gate), ctypes.c_longlong(gate.stride(0)),
+                               _ptr(gain), _ptr(y), ctypes.c_longlong(y.stride(0)), _dt(y, "gated_norm output"), T,
+                               int(groups), int(width), ctypes.c_float(eps), {"silu": 0, "sigmoid": 1}[act], _stream())
+    _check(lib, code, f"gated_norm (width {width})")
+
+
+def rotary_kv(x, positions, freq, mult, dims, norm_eps, q_out, cache, slots, n_heads, n_kv_heads, dim, v_dim,
+              page_size):
+    """Turn the queries and keys of float32 rows x [T, H*dim | G*dim | G*v_dim] by their positions
+    (freq: float64 [dims/2] turns per position of each pair, cos and sin times mult), divide each
+    head by its root mean square when norm_eps is not None, write the queries to q_out [T, H*dim]
+    and the keys and values into the cache's pages [n_pages, G*page_size*(dim+v_dim)] at slots."""
+    _need_cuda(x, positions, freq, q_out, cache, slots)
+    T = q_out.shape[0]
+    _f32_rows(x, "rotary_kv: x", (n_heads + n_kv_heads) * dim + n_kv_heads * v_dim)
+    _i32(positions, "positions")
+    _i32(slots, "slots")
+    if freq.dtype != torch.float64 or freq.numel() != dims // 2 or not freq.is_contiguous():
+        raise KernelError("rotary_kv: one float64 frequency per turned pair")
+    if q_out.shape[1] != n_heads * dim or q_out.stride(1) != 1 or q_out.dtype != cache.dtype or not cache.is_contiguous():
+        raise KernelError("rotary_kv: queries [T, H*dim] and the cache have one dtype")
+    n_pages = cache.shape[0]
+    if cache.numel() != n_pages * n_kv_heads * page_size * (dim + v_dim):
+        raise KernelError(f"rotary_kv: cache {tuple(cache.shape)} does not fit {n_kv_heads} heads of {dim}+{v_dim}")
+    lib = build.load("rotary")
+    code = lib.sglc_rotary_kv(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(positions), _ptr(freq), ctypes.c_float(mult),
+                              int(dims), 0 if norm_eps is None else 1, ctypes.c_float(norm_eps or 0.0), _ptr(q_out),
+                              ctypes.c_longlong(q_out.stride(0)), _ptr(cache), _ptr(slots), T, int(n_heads),
+                              int(n_kv_heads), int(dim), int(v_dim), int(page_size), n_pages, _dt(q_out, "queries"),
+                              _ptr(tc_error_flag(x.device)), _stream())
+    _check(lib, code, f"rotary_kv (head {dim})")
+
+
+def attention_ext(q, cache, block_table, token_req, positions, out, n_heads, n_kv_heads, dim, v_dim, page_size,
+                  scale, window, chunk, sinks, max_keys, max_q_len=None):
+    """attention_simt's extended form: values of size v_dim beside keys of size dim (cache
+    [n_pages, G*page_size*(dim+v_dim)]: a page's keys, then its values), an optional chunk mask
+    (a query sees the keys of its own chunk of `chunk` positions) and an optional sink per head
+    (float32 [H]) in the softmax's denominator.  q [T, H*dim]; out [T, H*v_dim]."""
+    _need_cuda(q, cache, block_table, token_req, positions, out, sinks)
+    for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
+        _i32(t, nm)
+    T = q.shape[0]
+    n_pages = cache.shape[0]
+    if q.shape[1] != n_heads * dim or out.shape[1] != n_heads * v_dim or q.stride(1) != 1 or out.stride(1) != 1 \
+            or q.dtype != out.dtype or q.dtype != cache.dtype or not cache.is_contiguous():
+        raise KernelError("attention_ext: q [T, H*dim], out [T, H*v_dim] and the cache have one dtype")
+    if cache.numel() != n_pages * n_kv_heads * page_size * (dim + v_dim):
+        raise KernelError(f"attention_ext: cache {tuple(cache.shape)} does not fit {n_kv_heads} heads of {dim}+{v_dim}")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads):
+        raise KernelError("attention_ext: one float32 sink per head")
+    lib = build.load("attention_simt")
+    code = lib.sglc_attention_simt_ext(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table), block_table.stride(0),
+                                       _ptr(token_req), _ptr(positions), _ptr(out), out.stride(0), T, int(n_heads),
+                                       int(n_kv_heads), int(dim), int(v_dim), int(page_size), ctypes.c_float(scale),
+                                       int(window or 0), int(chunk or 0), _ptr(sinks), int(max_keys),
+                                       _dt(q, "attention q"), _dt(cache, "cache"), n_pages,
+                                       _ptr(tc_error_flag(q.device)), int(max_q_len) if max_q_len else 2, _stream())
+    _check(lib, code, f"attention_ext (head {dim}/{v_dim}, up to {max_keys} keys)")
+
+
+def gated_act(src, dst, weights=None, per=0):
+    """dst[r, j] = silu(src[r, j]) * src[r, F + j] (* weights[r, j // per]); src [rows, 2F] holds the
+    gate columns, then the up columns; weights: float32 [rows, F // per] or None."""
+    _need_cuda(src, dst, weights)
+    rows, F = dst.shape
+    if src.shape[1] != 2 * F or src.shape[0] < rows or src.stride(1) != 1 or dst.stride(1) != 1:
+        raise KernelError("gated_act: src [rows, 2F], dst [rows, F]")
+    if weights is not None:
+        _f32_rows(weights, "gated_act: weights")
+        if per <= 0 or F % per or weights.shape[1] != F // per or weights.shape[0] < rows:
+            raise KernelError("gated_act: one weight per row and block of `per` columns")
+    lib = build.load("elementwise")
+    code = lib.sglc_gated_act(_ptr(src), ctypes.c_longlong(src.stride(0)), _dt(src, "gated_act source"), _ptr(dst),
+                              ctypes.c_longlong(dst.stride(0)), _dt(dst, "gated_act destination"), rows, F,
+                              _ptr(weights), ctypes.c_longlong(weights.stride(0) if weights is not None else 0),
+                              int(per), _stream())
+    _check(lib, code, "gated_act")
+
+
+ROUTER_MAX_EXPERTS = 256
+
+
+def router(logits, correction, dense, ids, weights, top, n_groups=1, keep=1, renorm=False, weight_scale=1.0):
+    """Sigmoid routing with a choice correction and group limits (see router.cu).  logits: float32
+    [T, E]; correction: float32 [E] or None; dense: float32 [T, E] (weights, zero where not
+    chosen); ids int32 [T, top]; weights float32 [T, top]."""
+    _need_cuda(logits, correction, dense, ids, weights)
+    T, E = dense.shape
+    _f32_rows(logits, "router: logits", E)
+    _f32_rows(dense, "router: dense", E)
+    if ids.dtype != torch.int32 or not ids.is_contiguous() or tuple(ids.shape) != (T, top) \
+            or weights.dtype != torch.float32 or not weights.is_contiguous() or tuple(weights.shape) != (T, top):
+        raise KernelError("router: ids int32 [T, top], weights float32 [T, top]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E):
+        raise KernelError("router: one float32 correction per expert")
+    lib = build.load("router")
+    code = lib.sglc_router(_ptr(logits), ctypes.c_longlong(logits.stride(0)), _ptr(correction), _ptr(dense),
+                           ctypes.c_longlong(dense.stride(0)), _ptr(ids), _ptr(weights), T, E, int(top), int(n_groups),
+                           int(keep), 1 if renorm else 0, ctypes.c_float(weight_scale), _stream())
+    _check(lib, code, f"router ({E} experts, {top} chosen)")

@@ -1,0 +1,97 @@
+// Rotary positions for the queries and keys of a step, the unit-RMS norm behind them, and the
+// write of the new keys and values into their cache pages, in one launch.
+//
+// A head's first `dims` entries are turned in pairs (i, i + dims/2), the "rotate half" layout:
+//   (u, v) -> (u cos a - v sin a,  v cos a + u sin a),   a = position * f_i,
+// cos and sin both times `mult`; the remaining entries pass.  The frequencies f_i (dims/2 of
+// them, made once by the host in 64-bit, whatever scaling rule shaped them) arrive as a table;
+// the angle is formed in 64-bit and brought into one turn before the 32-bit sine and cosine.
+// With `norm` the turned head is divided by its root mean square (eps inside the root, no gain).
+//
+// Input: 32-bit rows x [T][..] holding H query heads of D, then G key heads of D, then G value
+// heads of V.  Queries leave as [T][H*D] in the activation precision; keys and values go to
+// cache[page][ G x page_size x D keys | G x page_size x V values ] at slots[t] = page *
+// page_size + offset (a page with equal D and V is the usual [2][G][page_size][D]).
+#include "common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+constexpr int ROT_WARPS = 4;
+constexpr int ROT_MAX_DIM = 512;
+
+template <typename TA>
+__global__ void __launch_bounds__(ROT_WARPS * 32)
+rotary_kv_kernel(const float* __restrict__ x, long long x_stride, const int* __restrict__ positions,
+                 const double* __restrict__ freq, float mult, int dims, int norm, float eps,
+                 TA* __restrict__ q_out, long long q_stride, TA* __restrict__ cache, const int* __restrict__ slots,
+                 int T, int H, int G, int D, int V, int page_size, int n_pages, int* err) {
+  __shared__ float buf[ROT_WARPS][ROT_MAX_DIM];
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_wait();
+  const int pos = positions[t];
+  const int slot = slots[t];
+  const int page = slot / page_size, off = slot % page_size;
+  const bool page_ok = slot >= 0 && sglc_index_ok(page, n_pages, err);
+  const size_t page_elems = (size_t)G * page_size * (D + V);
+  const float* xr = x + (size_t)t * x_stride;
+  const int half = dims / 2;
+  float* b = buf[warp];
+  for (int row = warp; row < H + 2 * G; row += ROT_WARPS) {
+    if (row >= H + G) {                        // a value head: copied
+      const int g = row - H - G;
+      if (page_ok) {
+        TA* dst = cache + (size_t)page * page_elems + (size_t)G * page_size * D + ((size_t)g * page_size + off) * V;
+        const float* src = xr + (size_t)(H + G) * D + (size_t)g * V;
+        for (int d = lane; d < V; d += 32) dst[d] = from_f32<TA>(src[d]);
+      }
+      continue;
+    }
+    const float* src = xr + (size_t)row * D;
+    float ss = 0.0f;
+    for (int i = lane; i < half; i += 32) {
+      double a = (double)pos * freq[i];
+      a -= floor(a * 0.15915494309189535) * 6.283185307179586;
+      float sn, cs;
+      sincosf((float)a, &sn, &cs);
+      sn *= mult; cs *= mult;
+      const float u = src[i], v = src[i + half];
+      const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+      b[i] = ru; b[i + half] = rv;
+      ss = fmaf(ru, ru, fmaf(rv, rv, ss));
+    }
+    for (int d = 2 * half + lane; d < D; d += 32) {
+      const float u = src[d];
+      b[d] = u;
+      ss = fmaf(u, u, ss);
+    }
+    ss = warp_sum(ss);
+    const float f = norm ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+    __syncwarp();
+    TA* dst = nullptr;
+    if (row < H) dst = q_out + (size_t)t * q_stride + (size_t)row * D;
+    else if (page_ok) dst = cache + (size_t)page * page_elems + ((size_t)(row - H) * page_size + off) * D;
+    if (dst)
+      for (int d = lane; d < D; d += 32) dst[d] = from_f32<TA>(b[d] * f);
+    __syncwarp();
+  }
+}
+
+SGLC_API int sglc_rotary_kv(const float* x, long long x_stride, const int* positions, const double* freq, float mult,
+                            int dims, int norm, float eps, void* q_out, long long q_stride, void* cache,
+                            const int* slots, int T, int H, int G, int D, int V, int page_size, int n_pages,
+                            int dtype, int* err, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (H <= 0 || G <= 0 || D <= 0 || V <= 0 || dims < 0 || dims > D || dims % 2 != 0 || page_size <= 0)
+    return SGLC_ERR_ARGUMENT;
+  if (D > ROT_MAX_DIM) return SGLC_ERR_UNSUPPORTED;
+  if (dtype == SGLC_F32)
+    return sglc_launch(rotary_kv_kernel<float>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, x, x_stride,
+                       positions, freq, mult, dims, norm, eps, (float*)q_out, q_stride, (float*)cache, slots, T, H, G,
+                       D, V, page_size, n_pages, err);
+  if (dtype == SGLC_BF16)
+    return sglc_launch(rotary_kv_kernel<__nv_bfloat16>, dim3(T), dim3(ROT_WARPS * 32), 0, stream, 1, true, x,
+                       x_stride, positions, freq, mult, dims, norm, eps, (__nv_bfloat16*)q_out, q_stride,
+                       (__nv_bfloat16*)cache, slots, T, H, G, D, V, page_size, n_pages, err);
+  return SGLC_ERR_ARGUMENT;
+}

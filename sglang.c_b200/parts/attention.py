@@ -182,3 +182,134 @@ class LatentAttention(Part):
         o = ctx.alloc((T, H * R), self.rt.act_dtype)
         ctx.rt.attend_shared(ctx, q, cache, grp, o, H, R, float(p["scale"]), p.get("window"))
         return self.out.forward(ctx, o, out=out, residual=residual)
+
+
+@register_part("mixer", "rotary_attention")
+class RotaryAttention(Part):
+    """Causal softmax attention with grouped key/value heads whose sizes are free: queries and
+    keys of `head_dim`, values of `v_dim`.  q, k, v are projections of h without biases (one product
+    with a 32-bit result); q and k are turned by a `rotary` position part built from `rotary`
+    (its params), then, with `qk_norm`, each head is divided by its root mean square (eps inside
+    the root, no gain); score = (q . k) * scale.  `chunk`: position i sees j <= i only if both lie
+    in the same chunk of so many positions, counted from position 0.  `window`: the usual sliding
+    window.  `sink`: a learned score per head that joins the softmax's denominator once (it has no
+    key and no value and is not scaled).  Query head i reads key/value head i / (n_heads / n_kv_heads).
+    The cache keeps turned, normalised keys and plain values, a page's keys ahead of its values.
+    params: size, n_heads, n_kv_heads, head_dim, v_dim, scale, rotary (dims, base, scaling) or None,
+    qk_norm, eps, chunk, window, sink."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, G, D, V = (params[k] for k in ("size", "n_heads", "n_kv_heads", "head_dim", "v_dim"))
+        d = {"q_weight": WeightDecl((H * D, E), "matrix"), "k_weight": WeightDecl((G * D, E), "matrix"),
+             "v_weight": WeightDecl((G * V, E), "matrix"), "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+        if params.get("sink"):
+            d["sink"] = WeightDecl((H,), "bias")
+        return d
+
+    def load(self, tensors, store):
+        from .registry import get_part
+        refs = [tensors[k] for k in ("q_weight", "k_weight", "v_weight")]
+        n = sum(r.tensor.shape[0] for r in refs)
+        pad = (-n) % 8
+        self.qkv = Linear(store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(
+            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0)), None)
+        self.out = Linear(store.matrix(tensors["out_weight"]), None)
+        self.sink = store.vector(tensors["sink"]) if self.params.get("sink") else None
+        rot = self.params.get("rotary") or {"dims": 0, "base": 10000.0, "scaling": None}
+        self.rotary = get_part("position", "rotary")(rot, self.rt)
+        self.rotary.load({}, store)
+
+    def cache_need(self):
+        p = self.params
+        return CacheNeed.paged_kv(p["n_kv_heads"], p["head_dim"], p.get("window"), v_dim=p["v_dim"], chunk=p.get("chunk"))
+
+    def workspace_per_token(self):
+        p = self.params
+        H, G, D, V = p["n_heads"], p["n_kv_heads"], p["head_dim"], p["v_dim"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        return 4 * ((H + G) * D + G * V + 8) + act * H * (D + V) + 1024
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        from ..csrc import ops
+        p = self.params
+        H, G, D, V = p["n_heads"], p["n_kv_heads"], p["head_dim"], p["v_dim"]
+        T = h.shape[0]
+        grp = ctx.group(cache.group)
+        pre = ctx.alloc((T, self.qkv.out_size), torch.float32)
+        self.qkv.forward(ctx, h, out=pre)
+        q = ctx.alloc((T, H * D), self.rt.act_dtype)
+        ops.rotary_kv(ctx.columns(pre, 0, (H + G) * D + G * V), ctx.positions, self.rotary.frequencies,
+                      self.rotary.multiplier, self.rotary.dims, float(p["eps"]) if p.get("qk_norm") else None, q,
+                      cache.tensor, grp.slots, H, G, D, V, grp.page_size)
+        o = ctx.alloc((T, H * V), self.rt.act_dtype)
+        ops.attention_ext(q, cache.tensor, grp.block_table, ctx.token_req, ctx.positions, o, H, G, D, V, grp.page_size,
+                          float(p["scale"]), p.get("window"), p.get("chunk"), self.sink, ctx.max_keys,
+                          max_q_len=ctx.max_q_len)
+        return self.out.forward(ctx, o, out=out, residual=residual)
+
+
+@register_part("mixer", "side_by_side")
+class SideBySideMixers(Part):
+    """Two mixers that read the same rows; the result is half the sum of their outputs, each first
+    RMS-normed over the model width with a gain of its own:
+        mix(h) = (rms_norm(left(h)) * g_left + rms_norm(right(h)) * g_right) / 2.
+    Each side keeps what it needs (the layer's cache need is the pair of theirs).  The halves are
+    folded into the gains at load, and each side's norm adds straight into the 32-bit stream.
+    params: size, eps, left: (kind, params), right: (kind, params); weights: the sides' own under
+    `left.` / `right.`, and `left_out`, `right_out`."""
+
+    SIDES = ("left", "right")
+
+    @classmethod
+    def _side_class(cls, params, side):
+        from .registry import get_part
+        kind, sub = params[side]
+        return get_part("mixer", kind), sub
+
+    @classmethod
+    def declare_weights(cls, params):
+        d = {}
+        for side in cls.SIDES:
+            klass, sub = cls._side_class(params, side)
+            d.update({f"{side}.{role}": decl for role, decl in klass.declare_weights(sub).items()})
+            d[f"{side}_out"] = WeightDecl((params["size"],), "norm_gain")
+        return d
+
+    def __init__(self, params, runtime):
+        super().__init__(params, runtime)
+        self.sides = []
+        for side in self.SIDES:
+            klass, sub = self._side_class(params, side)
+            self.sides.append(klass(sub, runtime))
+        self.graph_safe = all(getattr(m, "graph_safe", True) for m in self.sides)
+
+    def load(self, tensors, store):
+        self.gains = []
+        for side, part in zip(self.SIDES, self.sides):
+            part.load({role[len(side) + 1:]: ref for role, ref in tensors.items() if role.startswith(side + ".")}, store)
+            ref = tensors[f"{side}_out"]
+            self.gains.append(store.computed(ref.name + "/2", kind="vector", make=lambda r=ref: r.tensor.float() * 0.5))
+
+    def cache_need(self):
+        return tuple(m.cache_need() for m in self.sides)
+
+    def workspace_per_token(self):
+        return 4 * self.params["size"] + max(m.workspace_per_token() for m in self.sides)
+
+    def graph_bound(self, ctx):
+        asked = [b for b in (m.graph_bound(ctx) for m in self.sides) if b is not None]
+        return max(asked) if asked else None
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        from ..csrc import ops
+        if out is not None:
+            raise ValueError("side_by_side adds into the residual stream; it has no separate output")
+        T, E = h.shape[0], self.params["size"]
+        y = ctx.alloc((T, E), torch.float32)
+        inner = ctx.mark()
+        for part, binding, gain in zip(self.sides, cache, self.gains):
+            part.forward(ctx, h, residual=None, cache=binding, position=position, out=y)
+            ctx.release(inner)
+            ops.norm_rows(y, gain, None, float(self.params["eps"]), residual[:T], form="rms", add=True)
+        return residual

@@ -79,3 +79,30 @@ class SandwichNormBlock(Part):
         if mix is not None and not done:
             mix.finish(ctx, x)
         return x
+
+
+@register_part("block", "parallel_sublayers")
+class ParallelSublayersBlock(Part):
+    """One norm, both sublayers read it: h = norm1(x); x += mixer(h) + ffn(h).  The feed-forward
+    is there only if the layer has an `ffn`.  Each sublayer's last product adds into the 32-bit
+    stream from its epilogue (or, for a mixer that normalises its result, from that norm)."""
+
+    def workspace_per_token(self, layer):
+        act = 4 if self.rt.dtype == "float32" else 2
+        inner = layer.mixer.workspace_per_token()
+        if "ffn" in layer.parts:
+            inner = max(inner, layer.ffn.workspace_per_token())
+        return act * layer.norm1.params["size"] + inner
+
+    def forward(self, ctx, x, layer, cache, position=None):
+        T = x.shape[0]
+        mark = ctx.mark()
+        h = ctx.alloc((T, x.shape[1]), self.rt.act_dtype)
+        layer.norm1.forward(ctx, x, h)
+        inner = ctx.mark()
+        layer.mixer.forward(ctx, h, residual=x, cache=cache, position=position)
+        ctx.release(inner)
+        if "ffn" in layer.parts:
+            layer.ffn.forward(ctx, h, residual=x)
+        ctx.release(mark)
+        return x

@@ -67,3 +67,103 @@ class MLP(Part):
         else:
             self.up.forward(ctx, h, out=u, act=self.params["activation"])
         return self.down.forward(ctx, u, out=out, residual=residual)
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(Part):
+    """residual += (silu(h Wg^T + bg) * (h Wu^T + bu)) Wd^T + bd.  Gate and up projections are one
+    product; the gating runs on its result; the down projection adds into the stream.
+    params: size, inner_size, bias."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, F, bias = params["size"], params["inner_size"], params.get("bias", True)
+        d = {"gate_weight": WeightDecl((F, E), "matrix"), "up_weight": WeightDecl((F, E), "matrix"),
+             "down_weight": WeightDecl((E, F), "residual_matrix")}
+        if bias:
+            d.update({"gate_bias": WeightDecl((F,), "bias"), "up_bias": WeightDecl((F,), "bias"),
+                      "down_bias": WeightDecl((E,), "bias")})
+        return d
+
+    def load(self, tensors, store):
+        g, u = tensors["gate_weight"], tensors["up_weight"]
+        w = store.computed(g.name + "+" + u.name, lambda: torch.cat([g.tensor.float(), u.tensor.float()], 0))
+        b = None
+        if "gate_bias" in tensors:
+            bg, bu = tensors["gate_bias"], tensors["up_bias"]
+            b = store.computed(bg.name + "+" + bu.name, kind="vector",
+                               make=lambda: torch.cat([bg.tensor.float(), bu.tensor.float()]))
+        self.gate_up = Linear(w, b)
+        self.down = Linear(store.matrix(tensors["down_weight"]),
+                           store.vector(tensors["down_bias"]) if "down_bias" in tensors else None)
+
+    def workspace_per_token(self):
+        return (4 if self.rt.dtype == "float32" else 2) * 3 * self.params["inner_size"] + 512
+
+    def forward(self, ctx, h, residual, out=None):
+        from ..csrc import ops
+        T, F = h.shape[0], self.params["inner_size"]
+        gu = ctx.alloc((T, 2 * F), self.rt.act_dtype)
+        self.gate_up.forward(ctx, h, out=gu)
+        z = ctx.alloc((T, F), self.rt.act_dtype)
+        ops.gated_act(gu, z)
+        return self.down.forward(ctx, z, out=out, residual=residual)
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    """A mixture of `n_experts` small gated feed-forwards without biases, of which a token uses
+    `top`: residual += sum over the chosen e of w_e * Wd_e (silu(Wg_e h) * (Wu_e h)).
+    Routing: s = sigmoid(h Wr^T) in 32-bit; the choice goes by s + correction, the weights are s
+    itself (not renormalised); experts form `n_groups` equal groups of neighbours, a group scores
+    the sum of its two largest choice scores, and only experts of the `keep` best groups can be
+    chosen (the others count as minus infinity).
+    All experts' gate and up matrices are one product over the step's rows; the gating multiplies
+    each expert's block of columns by the token's weight for it, which is zero for an expert not
+    chosen; the down matrices, side by side, are one product whose contraction is the sum over
+    experts.  A step does the same launches whatever the routing says.
+    params: size, inner_size (an expert's), n_experts, top, n_groups, keep."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, F, X = params["size"], params["inner_size"], params["n_experts"]
+        d = {"router": WeightDecl((X, E), "matrix"), "correction": WeightDecl((X,), "bias")}
+        for e in range(X):
+            d.update({f"gate_{e}": WeightDecl((F, E), "matrix"), f"up_{e}": WeightDecl((F, E), "matrix"),
+                      f"down_{e}": WeightDecl((E, F), "residual_matrix")})
+        return d
+
+    def load(self, tensors, store):
+        X = self.params["n_experts"]
+        gates, ups, downs = ([tensors[f"{k}_{e}"] for e in range(X)] for k in ("gate", "up", "down"))
+        self.gate_up = Linear(store.computed("+".join(r.name for r in gates + ups),
+                                             lambda: torch.cat([r.tensor.float() for r in gates + ups], 0)), None)
+        self.down = Linear(store.computed("|".join(r.name for r in downs),
+                                          lambda: torch.cat([r.tensor.float() for r in downs], 1)), None)
+        rw = tensors["router"]
+        pad = (-X) % 8
+        self.router = Linear(store.computed(rw.name + f"+{pad}", lambda: torch.cat(
+            [rw.tensor.float(), torch.zeros(pad, rw.tensor.shape[1])], 0)), None)
+        self.correction = store.vector(tensors["correction"])
+
+    def workspace_per_token(self):
+        p = self.params
+        act = 4 if self.rt.dtype == "float32" else 2
+        X = p["n_experts"]
+        return act * 3 * X * p["inner_size"] + 4 * (2 * X + 8) + 8 * p["top"] + 1024
+
+    def forward(self, ctx, h, residual, out=None):
+        from ..csrc import ops
+        p = self.params
+        T, F, X, top = h.shape[0], p["inner_size"], p["n_experts"], p["top"]
+        z = ctx.alloc((T, self.router.out_size), torch.float32)
+        self.router.forward(ctx, h, out=z)
+        dense = ctx.alloc((T, X), torch.float32)
+        ids = ctx.alloc((T, top), torch.int32)
+        wts = ctx.alloc((T, top), torch.float32)
+        ops.router(ctx.columns(z, 0, X), self.correction, dense, ids, wts, top, p.get("n_groups", 1), p.get("keep", 1))
+        gu = ctx.alloc((T, 2 * X * F), self.rt.act_dtype)
+        self.gate_up.forward(ctx, h, out=gu)
+        a = ctx.alloc((T, X * F), self.rt.act_dtype)
+        ops.gated_act(gu, a, weights=dense, per=F)
+        return self.down.forward(ctx, a, out=out, residual=residual)

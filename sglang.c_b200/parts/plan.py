@@ -16,7 +16,8 @@ class WeightDecl:
     """One tensor a part needs.  `shape` is the shape in the file.  `init`
     names the tensor's role for random initialisation: "matrix",
     "residual_matrix" (a projection back into the residual stream),
-    "embedding", "bias", "norm_gain", "norm_bias".  `kind` is "float" or "int"
+    "embedding", "bias", "norm_gain", "norm_bias", "conv_taps" (the taps of a short convolution
+    over time, [channels, taps]).  `kind` is "float" or "int"
     (integer tables stay int32)."""
     shape: Tuple[int, ...]
     init: str

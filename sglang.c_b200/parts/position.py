@@ -56,3 +56,36 @@ class SinusoidalPositions(PositionEncoding):
 
     def inverse_wavelengths(self):
         return self.inv_freq
+
+
+@register_part("position", "rotary")
+class RotaryPositions(PositionEncoding):
+    """Rotary positions inside a mixer: the first `dims` entries of every query and key head are
+    turned in pairs (i, i + dims/2) by the angle position * f_i, f_i = base^(-2i/dims).
+    With `scaling` = {factor, original, fast, slow} (YaRN) a pair's frequency is blended between
+    f_i and f_i / factor: with pair(t) = dims ln(original / (2 pi t)) / (2 ln base) the pair index at
+    which `original` positions make t turns, lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)),
+    dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are both multiplied by
+    0.1 ln(factor) + 1.  The table is made once, in 64-bit; the mixer's kernel forms the angles.
+    A mixer builds this part from its own params (a model may turn each layer differently).
+    params: dims, base, scaling (None or the four numbers)."""
+
+    def load(self, tensors, store):
+        import math
+
+        import torch
+        dims, base, sc = int(self.params["dims"]), float(self.params["base"]), self.params.get("scaling")
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = base ** (-2.0 * i / dims) if dims else i
+        self.multiplier = 1.0
+        if sc and dims:
+            factor, orig = float(sc["factor"]), float(sc["original"])
+            pair = lambda turns: dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+            lo = max(math.floor(pair(float(sc["fast"]))), 0)
+            hi = min(math.ceil(pair(float(sc["slow"]))), dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            self.multiplier = 0.1 * math.log(factor) + 1.0
+        self.frequencies = f.contiguous().to(self.rt.device) if self.rt is not None else f
+        self.dims = dims

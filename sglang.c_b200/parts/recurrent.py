@@ -57,3 +57,138 @@ class MinGRU(Part):
         ops.mingru_scan(ctx.columns(pre, 0, W), ctx.columns(pre, W, 2 * W), ctx.columns(pre, 2 * W, 3 * W), y,
                         cache.tensor, ctx.q_start, ctx.state_slots, ctx.R, ctx.max_q_len, workspace=ws)
         return self.out.forward(ctx, y, out=out, residual=residual)
+
+
+def _stacked(store, refs):
+    """Projections that read the same rows, laid one under the other: one product."""
+    return store.computed("+".join(r.name for r in refs), lambda: torch.cat([r.tensor.float() for r in refs], 0))
+
+
+@register_part("mixer", "gated_delta")
+class GatedDeltaRule(Part):
+    """The gated delta rule: per head a matrix state S [dim x v_dim] that decays, is corrected
+    towards the current value along the current key, and is read with the query:
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    q, k (n_qk_heads x dim) and v (n_heads x v_dim) are projections of h that pass a causal
+    convolution of `conv` taps over time per channel and silu; q and k are then unit vectors per
+    head (eps 1e-6 inside the root), q times dim^(-1/2); head i reads q/k head i / (n_heads /
+    n_qk_heads).  beta = sigmoid(h Wb^T); g = exp(-exp(A_log) softplus(h Wa^T + dt_bias)).
+    Each head's o is divided by its root mean square (eps), times a gain of v_dim entries shared by
+    the heads, times silu(h Wg^T); then the output projection.  All projections are one product
+    with a 32-bit result; convolution, gates, state and output stage are 32-bit.  Kept per request:
+    S, and the last conv - 1 inputs of the convolution.
+    params: size, n_heads, n_qk_heads, dim, v_dim, conv, eps."""
+
+    UNIT_EPS = 1e-6
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, G, D, V, K = (params[k] for k in ("size", "n_heads", "n_qk_heads", "dim", "v_dim", "conv"))
+        return {"q_weight": WeightDecl((G * D, E), "matrix"), "q_conv": WeightDecl((G * D, K), "conv_taps"),
+                "k_weight": WeightDecl((G * D, E), "matrix"), "k_conv": WeightDecl((G * D, K), "conv_taps"),
+                "v_weight": WeightDecl((H * V, E), "matrix"), "v_conv": WeightDecl((H * V, K), "conv_taps"),
+                "beta_weight": WeightDecl((H, E), "matrix"), "a_weight": WeightDecl((H, E), "matrix"),
+                "A_log": WeightDecl((H,), "bias"), "dt_bias": WeightDecl((H,), "bias"),
+                "gate_weight": WeightDecl((H * V, E), "matrix"), "norm": WeightDecl((V,), "norm_gain"),
+                "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+
+    def load(self, tensors, store):
+        p = self.params
+        H, G, D, V = p["n_heads"], p["n_qk_heads"], p["dim"], p["v_dim"]
+        refs = [tensors[k] for k in ("q_weight", "k_weight", "v_weight", "gate_weight", "beta_weight", "a_weight")]
+        n = 2 * G * D + 2 * H * V + 2 * H
+        pad = (-n) % 8                     # whole 32-byte pieces of 32-bit results a row
+        self.inp = Linear(store.computed("+".join(r.name for r in refs) + f"+{pad}", lambda: torch.cat(
+            [r.tensor.float() for r in refs] + [torch.zeros(pad, refs[0].tensor.shape[1])], 0)), None)
+        conv = [tensors[k] for k in ("q_conv", "k_conv", "v_conv")]
+        self.taps = store.computed("+".join(r.name for r in conv), kind="vector",
+                                   make=lambda: torch.cat([r.tensor.float() for r in conv], 0))
+        self.A_log, self.dt_bias = store.vector(tensors["A_log"]), store.vector(tensors["dt_bias"])
+        self.norm = store.vector(tensors["norm"])
+        self.out = Linear(store.matrix(tensors["out_weight"]), None)
+        self.channels = 2 * G * D + H * V
+        self.segments = [(0, G, D, 1, D ** -0.5), (G * D, G, D, 1, 1.0), (2 * G * D, H, V, 0, 1.0)]
+
+    def cache_need(self):
+        p = self.params
+        C = 2 * p["n_qk_heads"] * p["dim"] + p["n_heads"] * p["v_dim"]
+        return (CacheNeed.state((p["n_heads"], p["dim"], p["v_dim"]), "float32"),
+                CacheNeed.state((max(p["conv"] - 1, 0), C), "float32"))
+
+    def workspace_per_token(self):
+        p = self.params
+        H, G, D, V = p["n_heads"], p["n_qk_heads"], p["dim"], p["v_dim"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        return 4 * (2 * G * D + 2 * H * V + 2 * H + 8) + 4 * (2 * G * D + H * V) + 8 * H + 4 * H * V + act * H * V + 2048
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        p = self.params
+        H, G, D, V = p["n_heads"], p["n_qk_heads"], p["dim"], p["v_dim"]
+        T, C = h.shape[0], self.channels
+        state, tail = cache
+        pre = ctx.alloc((T, self.inp.out_size), torch.float32)
+        self.inp.forward(ctx, h, out=pre)
+        y = ctx.alloc((T, C), torch.float32)
+        gates = ctx.alloc((T, 2 * H), torch.float32)
+        gate_col = C + H * V
+        ops.short_conv(pre, self.taps, tail.tensor, y, ctx.token_req, ctx.q_start, ctx.state_slots, ctx.R,
+                       self.segments, unit_eps=self.UNIT_EPS,
+                       gates=(H, gate_col, gate_col + H, self.A_log, self.dt_bias, gates))
+        o = ctx.alloc((T, H * V), torch.float32)
+        ops.matrix_state("delta", ctx.columns(y, 0, G * D), ctx.columns(y, G * D, 2 * G * D), ctx.columns(y, 2 * G * D, C),
+                         o, state.tensor, ctx.q_start, ctx.state_slots, ctx.R, H, G, D, V, gates=gates)
+        z = ctx.alloc((T, H * V), self.rt.act_dtype)
+        ops.gated_norm(o, ctx.columns(pre, C, C + H * V), self.norm, z, H, V, float(p["eps"]), "silu")
+        return self.out.forward(ctx, z, out=out, residual=residual)
+
+
+@register_part("mixer", "linear_decay_attention")
+class LinearDecayAttention(Part):
+    """Linear attention with a fixed decay per head (lightning attention): q = silu(h Wq^T),
+    k = silu(h Wk^T) (n_heads x dim), v = silu(h Wv^T) (n_heads x v_dim); per head
+    S <- decay_h S + k v^T, o = S^T q, no other scale.  The heads' results side by side are
+    RMS-normed together with a gain, multiplied by sigmoid(h Wg^T) and projected.  The state is
+    32-bit, starts at zero and is carried per request.
+    params: size, n_heads, dim, v_dim, decay (one number per head), eps."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        E, H, D, V = (params[k] for k in ("size", "n_heads", "dim", "v_dim"))
+        return {"q_weight": WeightDecl((H * D, E), "matrix"), "k_weight": WeightDecl((H * D, E), "matrix"),
+                "v_weight": WeightDecl((H * V, E), "matrix"), "gate_weight": WeightDecl((H * V, E), "matrix"),
+                "norm": WeightDecl((H * V,), "norm_gain"), "out_weight": WeightDecl((E, H * V), "residual_matrix")}
+
+    def load(self, tensors, store):
+        refs = [tensors[k] for k in ("q_weight", "k_weight", "v_weight", "gate_weight")]
+        self.inp = Linear(_stacked(store, refs), None)
+        self.norm = store.vector(tensors["norm"])
+        self.out = Linear(store.matrix(tensors["out_weight"]), None)
+        decay = [float(v) for v in self.params["decay"]]
+        if len(decay) != self.params["n_heads"]:
+            raise ValueError("linear_decay_attention: one decay per head")
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(self.rt.device)
+
+    def cache_need(self):
+        p = self.params
+        return CacheNeed.state((p["n_heads"], p["dim"], p["v_dim"]), "float32")
+
+    def workspace_per_token(self):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        act = 4 if self.rt.dtype == "float32" else 2
+        return 4 * (2 * H * D + 2 * H * V) + 4 * H * V + act * H * V + 1024
+
+    def forward(self, ctx, h, residual, cache, position=None, out=None):
+        p = self.params
+        H, D, V = p["n_heads"], p["dim"], p["v_dim"]
+        T = h.shape[0]
+        pre = ctx.alloc((T, 2 * H * D + 2 * H * V), torch.float32)
+        self.inp.forward(ctx, h, out=pre)
+        o = ctx.alloc((T, H * V), torch.float32)
+        ops.matrix_state("decay", ctx.columns(pre, 0, H * D), ctx.columns(pre, H * D, 2 * H * D),
+                         ctx.columns(pre, 2 * H * D, 2 * H * D + H * V), o, cache.tensor, ctx.q_start, ctx.state_slots,
+                         ctx.R, H, H, D, V, head_decay=self.decay, silu_in=True)
+        z = ctx.alloc((T, H * V), self.rt.act_dtype)
+        ops.gated_norm(o, ctx.columns(pre, 2 * H * D + H * V, 2 * H * D + 2 * H * V), self.norm, z, 1, H * V,
+                       float(p["eps"]), "sigmoid")
+        return self.out.forward(ctx, z, out=out, residual=residual)

@@ -49,6 +49,8 @@ def random_tensor(seed, name, decl, scheme, n_layers, vocab_size=None):
         a = rng.standard_normal(shape) * s
     elif decl.init == "bias":
         a = rng.standard_normal(shape) * std if scheme == "varied" else np.zeros(shape)
+    elif decl.init == "conv_taps":
+        a = rng.standard_normal(shape) * 0.4
     elif decl.init == "norm_gain":
         a = 1.0 + rng.standard_normal(shape) * 0.1 if scheme == "varied" else np.ones(shape)
     elif decl.init == "norm_bias":
