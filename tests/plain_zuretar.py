@@ -245,3 +245,8 @@ def forward(cfg, w, tokens, streams=None):
         if streams is not None:
             streams.append(x.copy())
     return rms_norm(x, w["final.norm"], cfg["norm"]["eps"]) @ w["head"].T
+
+
+def forward_dir(model_dir, tokens):
+    cfg, w = read_model_dir(model_dir)
+    return forward(cfg, w, tokens)
