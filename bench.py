@@ -18,7 +18,7 @@ requests) over its time, against the measured copy bandwidth; `points` has decod
 at batch 1 and 64, the true 32-bit path and the prefill through the C interface;
 `kernels` says where a decode and a
 prefill step's time goes, kernel by kernel.  `--full` adds medium and XL layer
-sizes and the mixed workload to `points`.  `--compare tukavik` measures, instead of all
+sizes and the mixed workload to `points`.  `--compare tukavik` (or `zuretar`, which adds that design as a third column) measures, instead of all
 this, a Tukavik model beside the GPT-2 model of the same layer sizes.
 """
 import argparse
@@ -701,10 +701,84 @@ def tukavik_step_bytes(cfg, batch, context, prompt_tokens):
     return out
 
 
-def compare_tukavik(sizes, steps, warmup, pk):
-    """Decode (batch 8 and 64 at context 512) and prefill (2 x 1,024 tokens) of a Tukavik model beside
-    the GPT-2 model of the same layer sizes, both through the Python engine's step function (the
-    native engine runs GPT-2's parts only), bfloat16, random weights; and each model's kernel table."""
+def zuretar_config(base, n_layer):
+    """A Zuretar model with the layer sizes of a GPT-2 model: the same width, depth, head size (64) and
+    vocabulary, and per token as many weights at work.  Layers in fours: a gated delta rule (as many
+    heads as the model, half as many query/key heads, keys and values of 64, four taps) with a gated
+    feed-forward of two thirds the width of GPT-2's (three matrices instead of two); the delta rule again
+    with a mixture of 8 experts of a third of that width, 2 chosen of the 2 best of 4 groups; softmax
+    attention (the model's heads over a quarter as many key/value heads, chunks of 256, a sink) beside a
+    linear attention of a quarter of the heads, with the experts; and a layer that runs the first one's
+    weights again."""
+    E, H, I = base["n_embd"], base["n_head"], base["n_inner"]
+    ff = max(64, (2 * I // 3) // 64 * 64)
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": max(64, (ff // 2) // 64 * 64)},
+           "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    delta = {"heads": H, "kv_heads": max(1, H // 2), "dim": 64, "vdim": 64, "conv": 4}
+    hq = max(1, H // 4)
+    par = {"left": {"heads": H, "kv_heads": hq, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 256},
+                    "rot": {"base": 10000.0, "dims": 64,
+                            "scaling": {"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}}},
+           "right": {"heads": hq, "dim": 64, "vdim": 64, "decay": [1.0 - 2.0 ** -(3 + i % 6) for i in range(hq)]}}
+    layers = []
+    for i in range(n_layer):
+        if i % 4 == 0:
+            layers.append({"type": "delta", "mixer": delta, "mlp": dense})
+        elif i % 4 == 1:
+            layers.append({"type": "delta", "mixer": delta, "mlp": moe})
+        elif i % 4 == 2:
+            layers.append({"type": "parallel", "mixer": par, "mlp": moe})
+        else:
+            layers.append({"type": "delta", "mixer": delta, "mlp": dense, "weights_of": i - 3})
+    return {"architecture": "Zuretar", "vocab": base["vocab_size"], "width": E, "norm": {"eps": 1e-5},
+            "layers": layers, "max_positions": base["n_positions"]}
+
+
+def zuretar_step_bytes(cfg, batch, context, prompt_tokens):
+    """What the kernels that only this design has must move in a step (32-bit projections, states and
+    read-outs; bfloat16 activations and cache): {decode | prefill: {kernel label: bytes}}."""
+    out = {}
+    for name, T, R in (("decode", batch, batch), ("prefill", prompt_tokens, 2)):
+        conv = state = gnorm = rot = attn = gact = 0
+        for layer in cfg["layers"]:
+            m = layer["mixer"]
+            if layer["type"] == "delta":
+                C = 2 * m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"]
+                conv += T * C * 8 + T * m["heads"] * 16 + R * (m["conv"] - 1) * C * 8
+                hv = m["heads"] * m["vdim"]
+                state += R * m["heads"] * m["dim"] * m["vdim"] * 8 + T * (C + hv) * 4
+                gnorm += T * hv * (8 + 2)
+            else:
+                le, ri = m["left"], m["right"]
+                row = (le["heads"] + le["kv_heads"]) * le["dim"] + le["kv_heads"] * le["vdim"]
+                rot += T * row * (4 + 2)
+                kv = le["kv_heads"] * (le["dim"] + le["vdim"]) * 2
+                seen = min(context, le["mask"]["size"]) if name == "decode" else le["mask"]["size"] // 2 // 8
+                attn += T * seen * kv + T * le["heads"] * (le["dim"] + le["vdim"]) * 2
+                hv = ri["heads"] * ri["vdim"]
+                state += R * ri["heads"] * ri["dim"] * ri["vdim"] * 8 + T * (2 * ri["heads"] * ri["dim"] + 2 * hv) * 4
+                gnorm += T * hv * (8 + 2)
+            mlp = layer["mlp"]
+            if mlp:
+                F = mlp["ff"] if mlp["kind"] == "dense" else mlp["expert"]["ff"] * mlp["router"]["experts"]
+                gact += T * F * 6
+        out[name] = {"short_conv": conv, "matrix_state": state, "gated_norm": gnorm, "rotary_kv": rot,
+                     "attention_ext": attn, "gated_act": gact}
+    return out
+
+
+DESIGNS = {"tukavik": (tukavik_config, tukavik_step_bytes,
+                       {"mingru_scan": "mingru_scan", "norm_rows": "norm_rows", "depth_mix": "depth_mix",
+                        "attention_decode_shared": "attention_shared"}),
+           "zuretar": (zuretar_config, zuretar_step_bytes,
+                       {k: k for k in ("short_conv", "matrix_state", "gated_norm", "rotary_kv", "attention_ext", "gated_act")})}
+
+
+def compare_designs(designs, sizes, steps, warmup, pk):
+    """Decode (batch 8 and 64 at context 512) and prefill (2 x 1,024 tokens) of a model of each named
+    design beside the GPT-2 model of the same layer sizes, all through the Python engine's step function
+    (the native engine runs GPT-2's parts only), bfloat16, random weights; and each model's kernel table."""
     import torch
     from sglang_c_b200.config import resolve_architecture
     from sglang_c_b200.engine import Engine
@@ -714,10 +788,10 @@ def compare_tukavik(sizes, steps, warmup, pk):
         base = MODELS[size]
         n_layer = base["n_layer"]
         row = {}
-        for design in ("gpt2", "tukavik"):
+        for design in ["gpt2"] + list(designs):
             tmp = tempfile.mkdtemp(prefix="sglc_bench_")
             atexit.register(shutil.rmtree, tmp, True)
-            cfg_d = dict(base) if design == "gpt2" else tukavik_config(base, n_layer)
+            cfg_d = dict(base) if design == "gpt2" else DESIGNS[design][0](base, n_layer)
             arch = resolve_architecture(cfg_d)
             model_dir = write_random_model(os.path.join(tmp, "model"), arch, arch.config_class.from_dict(cfg_d), 1234,
                                            scheme="standard", store_dtype="bfloat16")
@@ -731,12 +805,11 @@ def compare_tukavik(sizes, steps, warmup, pk):
             dms = time_prefill(eng, 2, PREFILL_TOKENS // 2, 3, behind_sleep=True)
             r["prefill"] = {"tok_s": PREFILL_TOKENS / (dms / 1e3), "device_ms": dms}
             r["kernels"] = kernel_table(eng, BATCH, CONTEXT, PREFILL_TOKENS // 2)
-            if design == "tukavik":
-                nb = tukavik_step_bytes(cfg_d, BATCH, CONTEXT, PREFILL_TOKENS)
+            if design != "gpt2":
+                nb = DESIGNS[design][1](cfg_d, BATCH, CONTEXT, PREFILL_TOKENS)
                 for kind in ("decode", "prefill"):
                     for label, k in r["kernels"][kind].items():
-                        key = {"mingru_scan": "mingru_scan", "norm_rows": "norm_rows", "depth_mix": "depth_mix",
-                               "attention_decode_shared": "attention_shared"}.get(label)
+                        key = DESIGNS[design][2].get(label)
                         if key and k["us"] > 0:
                             k["bytes"] = nb[kind][key]
                             k["frac_of_copy"] = round(nb[kind][key] / (k["us"] * 1e-6) / 1e9 / pk["hbm_gbs"], 4)
@@ -825,7 +898,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "fp32"],
                     help="a handful of steps of one kind and nothing else (what a profiler is pointed at): "
                          "decode steps at batch 8, prefill steps of 2 x 1,024 tokens, or both on the 32-bit path")
-    ap.add_argument("--compare", default=None, choices=["tukavik"],
+    ap.add_argument("--compare", default=None, choices=["tukavik", "zuretar"],
                     help="nothing of the above: decode and prefill of a model of this design beside the GPT-2 model "
                          "of equal layer sizes (--model, or small and medium with --full), with both kernel tables")
     args = ap.parse_args()
@@ -845,8 +918,10 @@ def main():
     if args.compare:
         clocks = ClockSampler()
         clocks.start()
-        res = compare_tukavik(["small", "medium"] if args.full else [args.model], steps, warmup, pk)
-        print(json.dumps({"metric": "decode and prefill tok/s, Tukavik beside GPT-2 at equal layer sizes (Python engine)",
+        designs = ["tukavik", "zuretar"] if args.compare == "zuretar" else ["tukavik"]
+        res = compare_designs(designs, ["small", "medium"] if args.full else [args.model], steps, warmup, pk)
+        print(json.dumps({"metric": f"decode and prefill tok/s, {' and '.join(d.capitalize() for d in designs)} beside "
+                                    "GPT-2 at equal layer sizes (Python engine)",
                           "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "steps": steps, "warmup": warmup,
                           "data": "synthetic: seeded random weights and uniform random token ids",
                           "peaks": pk, "sizes": res, "clocks": clocks.stop()}))

@@ -62,6 +62,8 @@ struct Args {
   int split_min;          // key tiles from which a query tile is shared by the cluster's two blocks
   int* err;
   int kv_shared;          // pages [1][Hkv][page_size][D]: one block of rows serves as keys and as values
+  int chunk;              // > 0: a query sees only the keys of its own chunk of so many positions (counted from 0)
+  const float* sinks;     // [H] or null: a score per head that joins the softmax's denominator once, unscaled
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -84,7 +86,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // byte offset of 16-byte chunk `c` (0..7) of row `r` in a [rows][128 B] tile with the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
-template <int D>
+// EXT: the instantiation that also knows a chunk mask and sinks (Args::chunk, Args::sinks); the
+// plain one is compiled without either.
+template <int D, bool EXT>
 __global__ void __launch_bounds__(THREADS, (D == 64 ? 2 : 1))
 attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_kv, const Args a) {
@@ -134,6 +138,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     const int lp = p0 + min(BQ, q_len - t * BQ) - 1;
     int fk = 0;
     if (a.window > 0 && p0 - a.window + 1 > 0) fk = p0 - a.window + 1;
+    if (EXT && a.chunk > 0) fk = max(fk, p0 / a.chunk * a.chunk);       // (the first row's chunk starts first)
     first_tile = fk / BKV;
     return lp / BKV - first_tile + 1;
   };
@@ -170,6 +175,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   const int last_pos = pos0 + rows - 1;
   int first_key = 0;
   if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
+  if (EXT && a.chunk > 0) first_key = max(first_key, pos0 / a.chunk * a.chunk);
   int kt_first;
   const int n_all = key_tiles(qt, kt_first);
   // rank 1's half ends with the masked tile at the diagonal, which costs more than a plain one:
@@ -372,7 +378,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     const int pos_r[2] = {pos0 + row_r[0], pos0 + row_r[1]};
     int lo_r[2];
 #pragma unroll
-    for (int x = 0; x < 2; x++) lo_r[x] = (a.window > 0 && pos_r[x] - a.window + 1 > 0) ? pos_r[x] - a.window + 1 : 0;
+    for (int x = 0; x < 2; x++) {
+      lo_r[x] = (a.window > 0 && pos_r[x] - a.window + 1 > 0) ? pos_r[x] - a.window + 1 : 0;
+      if (EXT && a.chunk > 0) lo_r[x] = max(lo_r[x], pos_r[x] / a.chunk * a.chunk);
+    }
     const uint32_t tS = tmem_base + ((uint32_t)lane0 << 16);
     const uint32_t tO = tS + 128;
     const int st = threadIdx.x;                                 // 0..SOFTMAX_THREADS-1
@@ -403,7 +412,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       // a tile needs the mask only where it meets the diagonal, the window's edge or the end
       // of the rows; elsewhere every key is visible to every row of the tile
       const bool full_tile = (key0 + BKV - 1 <= pos0) && (rows == BQ) &&
-                             (a.window <= 0 || key0 >= pos0 + BQ - a.window);
+                             (a.window <= 0 || key0 >= pos0 + BQ - a.window) &&
+                             (!EXT || a.chunk <= 0 || key0 >= (pos0 + BQ - 1) / a.chunk * a.chunk);
       // On such a tile row x sees the keys vis_first[x] .. vis_first[x] + vis_span[x], counted
       // from the tile's first key (a row that sees none: a first key beyond every tile).  With
       // rel = key - first, "visible" is one unsigned comparison: rel <= span.
@@ -530,6 +540,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
           a1[x] = exp2f((m[x] - m_use) * a.scale_log2);
           a2[x] = exp2f((m2[x] - m_use) * a.scale_log2);
           l[x] = l[x] * a1[x] + l2[x] * a2[x];
+          if (EXT) m[x] = mm;
         }
 #pragma unroll
         for (int c = 0; c < HP; c++) {
@@ -558,7 +569,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
       for (int x = 0; x < 2; x++) {
         if (!valid_r[x]) continue;
-        const float inv = 1.0f / l[x];
+        float inv = 1.0f / l[x];
+        if (EXT && a.sinks) {                            // exp(sink - max) joins the sum; the maximum may become the sink
+          const float sk = a.sinks[h] * 1.4426950408889634f, ms = m[x] * a.scale_log2, top = fmaxf(ms, sk);
+          const float keep = exp2f(ms - top);
+          inv = keep / (l[x] * keep + exp2f(sk - top));
+        }
         __nv_bfloat16* op = a.out + (size_t)(t0 + qt * BQ + row_r[x]) * a.o_stride + (size_t)h * D + 2 * q4;
 #pragma unroll
         for (int i = 0; i < D / 8; i++) {          // the row's i-th block of 8 columns
@@ -632,22 +648,22 @@ bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int
   return true;
 }
 
-template <int D>
+template <int D, bool EXT>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Args& a, int R, int max_q_len,
            cudaStream_t stream) {
   constexpr int DB = D / 64;
   size_t smem = (size_t)BQ * 128 * DB + (size_t)BQ * 128 * 2 + (size_t)2 * KV_STAGES * BKV * 128 * DB + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, EXT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(attention_prefill_kernel<D, EXT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   dim3 grid(a.H * R, (max_q_len + BQ - 1) / BQ, 2);      // two blocks (one cluster) per query tile
-  return sglc_launch(attention_prefill_kernel<D>, grid, dim3(THREADS), smem, stream, 2, true, mq, mkv, a);
+  return sglc_launch(attention_prefill_kernel<D, EXT>, grid, dim3(THREADS), smem, stream, 2, true, mq, mkv, a);
 }
 }  // namespace
 
@@ -668,8 +684,10 @@ static int attention_prefill_run(const void* q, int q_stride, const void* cache,
                                  const int* kv_len, void* out, int o_stride, int R,
                                  int max_q_len, int H, int Hkv, int D, int page_size,
                                  float scale, int window, int T, int n_pages, int skip_single,
-                                 int* err, int kv_shared, cudaStream_t stream) {
+                                 int* err, int kv_shared, cudaStream_t stream, int chunk = 0,
+                                 const float* sinks = nullptr) {
   if (R <= 0 || max_q_len <= 0) return SGLC_OK;
+  if (chunk < 0) return SGLC_ERR_ARGUMENT;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0) return SGLC_ERR_ARGUMENT;
   if (!(D == 64 || D == 128) || H > 65535 || R > 32767 || max_q_len > 65535 * BQ || !(scale > 0.0f)) return SGLC_ERR_UNSUPPORTED;
   if (q_stride % 8 != 0 || o_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
@@ -688,6 +706,8 @@ static int attention_prefill_run(const void* q, int q_stride, const void* cache,
   a.skip_single = skip_single;
   a.split_min = g_split_min;
   a.kv_shared = kv_shared;
+  a.chunk = chunk;
+  a.sinks = sinks;
   // TMA needs whole pages inside a 128-key tile and rows it can address
   CUtensorMap mq, mkv;
   memset(&mq, 0, sizeof(mq));
@@ -698,8 +718,12 @@ static int attention_prefill_run(const void* q, int q_stride, const void* cache,
               get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages, kv_shared ? 1 : 2);
     a.use_tma = ok ? 1 : 0;
   }
-  if (D == 64) return launch<64>(mq, mkv, a, R, max_q_len, stream);
-  return launch<128>(mq, mkv, a, R, max_q_len, stream);
+  if (chunk > 0 || sinks) {
+    if (D == 64) return launch<64, true>(mq, mkv, a, R, max_q_len, stream);
+    return launch<128, true>(mq, mkv, a, R, max_q_len, stream);
+  }
+  if (D == 64) return launch<64, false>(mq, mkv, a, R, max_q_len, stream);
+  return launch<128, false>(mq, mkv, a, R, max_q_len, stream);
 }
 
 SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* cache,
@@ -724,4 +748,18 @@ SGLC_API int sglc_attention_prefill_tc_shared(const void* q, int q_stride, const
   return attention_prefill_run(q, q_stride, cache, block_table, bt_stride, q_start, kv_len, out, o_stride, R,
                                max_q_len, H, Hkv, D, page_size, scale, window, T, n_pages, skip_single, err, 1,
                                stream);
+}
+
+// The same with a chunk mask (chunk > 0: a query sees only the keys of its own chunk of so many
+// positions, counted from position 0) and a sink per head (sinks: float [H] or null) in the
+// softmax's denominator.
+SGLC_API int sglc_attention_prefill_tc_ext(const void* q, int q_stride, const void* cache,
+                                           const int* block_table, int bt_stride, const int* q_start,
+                                           const int* kv_len, void* out, int o_stride, int R,
+                                           int max_q_len, int H, int Hkv, int D, int page_size,
+                                           float scale, int window, int chunk, const float* sinks, int T,
+                                           int n_pages, int skip_single, int* err, cudaStream_t stream) {
+  return attention_prefill_run(q, q_stride, cache, block_table, bt_stride, q_start, kv_len, out, o_stride, R,
+                               max_q_len, H, Hkv, D, page_size, scale, window, T, n_pages, skip_single, err, 0,
+                               stream, chunk, sinks);
 }

@@ -9,18 +9,22 @@
 //
 // Column j of S needs nothing of the other columns: S^T k, the update and S^T q are, per column,
 // two dot products and one scaled addition over D.  So a column belongs to L lanes of one warp that
-// keep it in registers (32 entries each, D <= 32 L, entry e of lane s is row e L + s), a block
+// keep it in registers (PER entries each, D <= PER L, entry e of lane s is row PER s + e), a block
 // takes a range of columns of one (request, head), and the tokens go by one after the other; the
-// block stages the next tokens' q, k, v and gates in shared memory, eight at a time.
+// block stages the next tokens' q, k, v and gates in shared memory, a batch at a time, while it
+// works on the batch before.  A token's time is the time of one warp's chain of dependent
+// instructions (measured: 250-290 ns a token at a key size of 64 whether a lane keeps 4, 8 or 16
+// entries; 170 ns without the delta rule's first dot product).  PER = 16 costs the fewest
+// instructions in all; key sizes of 33..64 take PER = 8 in steps with few (request, head) pairs,
+// where it was a tenth faster.
 // q and k may have fewer heads than v (head h reads q/k head h / (H / G)).
 // With `silu_in` the kernel applies silu to q, k and v as it stages them.
 #include "common.cuh"
 
 SGLC_DEFINE_ERROR_STRING()
 
-constexpr int MS_PER = 32;        // entries of a column a lane keeps
-constexpr int MS_BATCH = 8;       // tokens staged at a time
-constexpr int MS_MAX_THREADS = 128;
+constexpr int MS_UNROLL = 8;      // tokens worked on without a loop between them
+constexpr int MS_MAX_DIM = 256;   // key sizes up to 16 entries a lane x 16 lanes
 
 enum { MS_DECAY = 0, MS_DELTA = 1 };
 
@@ -33,26 +37,37 @@ struct MsArgs {
   float* out; long long out_stride;       // [T][H*V]
   float* state;                           // [n_slots][H][D][V]
   const int* q_start; const int* state_slots;
-  int R, H, G, D, V, n_slots, cols;       // cols: columns a block takes
+  int R, H, G, D, V, n_slots;
   int silu_in;
   int* err;
 };
 
 __device__ __forceinline__ float ms_silu(float v) { return v / (1.0f + expf(-v)); }
 
-template <int L, int MODE>
-__global__ void __launch_bounds__(MS_MAX_THREADS)
+// L lanes a column, NW warps a block (each warp its own 32 / L columns of one head; the block
+// stages q and k once for all of them).  While a batch of tokens is worked on, the next batch's
+// loads are in flight into registers; they go to the other half of the staging buffers behind
+// the one barrier a batch needs.
+template <int MS_PER, int L, int NW, int MODE>
+__global__ void __launch_bounds__(32 * NW)
 matrix_state_kernel(MsArgs p) {
-  constexpr int DP = MS_PER * L;
-  extern __shared__ __align__(16) float sm[];
-  float* ks = sm;                          // [BATCH][DP]
-  float* qs = ks + MS_BATCH * DP;          // [BATCH][DP]
-  float* vs = qs + MS_BATCH * DP;          // [BATCH][cols]
-  float* gs = vs + MS_BATCH * p.cols;      // [BATCH][2]
+  // (a lane's entries of q and k lie together in shared memory, 16-byte loads; the stride between
+  // lanes is chosen so that the lanes of a quarter warp fall on different banks)
+  constexpr int DP = MS_PER * L, THREADS = 32 * NW, COLS = 32 / L * NW, LP = MS_PER == 4 ? 4 : MS_PER + 4, SP = L * LP;
+  // Tokens staged at a time: as many as the 48 KB of static shared memory hold, up to 32.  (The loads of a batch are
+  // in flight while the batch before is worked on: a batch must take longer than a load's way from
+  // memory, about 2 us, or the tokens wait for it; 8 tokens did not.)
+  constexpr int FIT = 6144 / (2 * SP + COLS + 2) / 8 * 8;          // (two halves of q, k, v and gates in 48 KB)
+  constexpr int MS_BATCH = FIT >= 32 ? 32 : (FIT >= 8 ? FIT : 8);
+  constexpr int NG = (2 * MS_BATCH + THREADS - 1) / THREADS;
+  constexpr int NK = (MS_BATCH * DP + THREADS - 1) / THREADS;      // q/k entries a thread stages per batch
+  constexpr int NV = (MS_BATCH * COLS + THREADS - 1) / THREADS;    // v entries
+  __shared__ __align__(16) float ks[2][MS_BATCH * SP], qs[2][MS_BATCH * SP];
+  __shared__ float vs[2][MS_BATCH * COLS], gs[2][2 * MS_BATCH];
   pdl_launch_dependents();
   const int r = blockIdx.x, h = blockIdx.y, g = h / (p.H / p.G);
-  const int tid = threadIdx.x, sub = tid % L, col = blockIdx.z * p.cols + tid / L;
-  const bool on = tid / L < p.cols && col < p.V;
+  const int tid = threadIdx.x, sub = tid % L, lcol = tid / L, col = blockIdx.z * COLS + lcol;
+  const bool on = col < p.V;
   pdl_wait();
   const int t0 = p.q_start[r], t1 = p.q_start[r + 1];
   const int slot = p.state_slots[r];
@@ -61,46 +76,76 @@ matrix_state_kernel(MsArgs p) {
   float S[MS_PER];
 #pragma unroll
   for (int e = 0; e < MS_PER; e++) {
-    const int i = e * L + sub;
+    const int i = sub * MS_PER + e;
     S[e] = (on && i < p.D) ? sp[(size_t)i * p.V + col] : 0.0f;
   }
   const float hd = MODE == MS_DECAY ? p.head_decay[h] : 0.0f;
-  for (int tb = t0; tb < t1; tb += MS_BATCH) {
-    const int nb = min(MS_BATCH, t1 - tb);
-    __syncthreads();
-    for (int x = tid; x < MS_BATCH * DP; x += blockDim.x) {
-      const int b = x / DP, i = x % DP;
-      float kv = 0.0f, qv = 0.0f;
-      if (b < nb && i < p.D) {
-        kv = p.k[(size_t)(tb + b) * p.k_stride + (size_t)g * p.D + i];
-        qv = p.q[(size_t)(tb + b) * p.q_stride + (size_t)g * p.D + i];
-        if (p.silu_in) { kv = ms_silu(kv); qv = ms_silu(qv); }
-      }
-      ks[x] = kv;
-      qs[x] = qv;
-    }
-    for (int x = tid; x < MS_BATCH * p.cols; x += blockDim.x) {
-      const int b = x / p.cols, c = blockIdx.z * p.cols + x % p.cols;
-      float vv = 0.0f;
-      if (b < nb && c < p.V) {
-        vv = p.v[(size_t)(tb + b) * p.v_stride + (size_t)h * p.V + c];
-        if (p.silu_in) vv = ms_silu(vv);
-      }
-      vs[x] = vv;
-    }
-    if (MODE == MS_DELTA && tid < 2 * MS_BATCH) {
-      const int b = tid >> 1, which = tid & 1;
-      gs[tid] = b < nb ? p.gates[(size_t)(tb + b) * p.gates_stride + which * p.H + h] : 0.0f;
-    }
-    __syncthreads();
-    for (int b = 0; b < nb; b++) {
-      const float* kr = ks + b * DP + sub;
-      const float* qr = qs + b * DP + sub;
-      const float vv = vs[b * p.cols + min(tid / L, p.cols - 1)];
-      float kk[MS_PER];
+  float* out_row = p.out + (size_t)h * p.V + col;
+  float rk[NK], rq[NK], rv[NV], rg[NG];
+  auto fetch = [&](int tb) {                 // a batch's inputs into registers (zeros beyond the request's end)
 #pragma unroll
-      for (int e = 0; e < MS_PER; e++) kk[e] = kr[e * L];
-      float o = 0.0f;
+    for (int n = 0; n < NK; n++) {
+      const int x = tid + n * THREADS, b = x / DP, i = x % DP;
+      const bool in = x < MS_BATCH * DP && tb + b < t1 && i < p.D;
+      rk[n] = in ? __ldg(p.k + (size_t)(tb + b) * p.k_stride + (size_t)g * p.D + i) : 0.0f;
+      rq[n] = in ? __ldg(p.q + (size_t)(tb + b) * p.q_stride + (size_t)g * p.D + i) : 0.0f;
+    }
+#pragma unroll
+    for (int n = 0; n < NV; n++) {
+      const int x = tid + n * THREADS, b = x / COLS, c = blockIdx.z * COLS + x % COLS;
+      rv[n] = (x < MS_BATCH * COLS && tb + b < t1 && c < p.V)
+                  ? __ldg(p.v + (size_t)(tb + b) * p.v_stride + (size_t)h * p.V + c) : 0.0f;
+    }
+    if (MODE == MS_DELTA) {
+      // (beyond the request's end: step size 0, decay 1: such a token leaves the state as it is)
+#pragma unroll
+      for (int n = 0; n < NG; n++) {
+        const int x = tid + n * THREADS, b = x >> 1, which = x & 1;
+        rg[n] = (x < 2 * MS_BATCH && tb + b < t1) ? __ldg(p.gates + (size_t)(tb + b) * p.gates_stride + which * p.H + h)
+                                                  : (float)which;
+      }
+    }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int n = 0; n < NK; n++) {
+      const int x = tid + n * THREADS;
+      if (x < MS_BATCH * DP) {
+        const int b = x / DP, i = x % DP, at = b * SP + i / MS_PER * LP + i % MS_PER;
+        ks[buf][at] = p.silu_in ? ms_silu(rk[n]) : rk[n];
+        qs[buf][at] = p.silu_in ? ms_silu(rq[n]) : rq[n];
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NV; n++) {
+      const int x = tid + n * THREADS;
+      if (x < MS_BATCH * COLS) vs[buf][x] = p.silu_in ? ms_silu(rv[n]) : rv[n];
+    }
+    if (MODE == MS_DELTA) {
+#pragma unroll
+      for (int n = 0; n < NG; n++)
+        if (tid + n * THREADS < 2 * MS_BATCH) gs[buf][tid + n * THREADS] = rg[n];
+    }
+  };
+  fetch(t0);
+  int buf = 0;
+  for (int tb = t0; tb < t1; tb += MS_BATCH, buf ^= 1) {
+    const int nb = min(MS_BATCH, t1 - tb);
+    stage(buf);
+    __syncthreads();           // the batch is staged; everybody is done with the other half's last batch
+    if (tb + MS_BATCH < t1) fetch(tb + MS_BATCH);
+    auto token = [&](int b) {
+      const float4* kr = reinterpret_cast<const float4*>(ks[buf] + b * SP + sub * LP);
+      const float4* qr = reinterpret_cast<const float4*>(qs[buf] + b * SP + sub * LP);
+      const float vv = vs[buf][b * COLS + lcol];
+      float kk[MS_PER], qq[MS_PER];
+#pragma unroll
+      for (int e = 0; e < MS_PER; e += 4) {
+        const float4 k4 = kr[e / 4], q4 = qr[e / 4];
+        kk[e] = k4.x; kk[e + 1] = k4.y; kk[e + 2] = k4.z; kk[e + 3] = k4.w;
+        qq[e] = q4.x; qq[e + 1] = q4.y; qq[e + 2] = q4.z; qq[e + 3] = q4.w;
+      }
+      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
       if (MODE == MS_DELTA) {
         float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
 #pragma unroll
@@ -113,58 +158,74 @@ matrix_state_kernel(MsArgs p) {
         float dk = (d0 + d1) + (d2 + d3);
 #pragma unroll
         for (int m = 1; m < L; m <<= 1) dk += __shfl_xor_sync(0xffffffffu, dk, m);
-        const float beta = gs[2 * b], gd = gs[2 * b + 1];
+        const float beta = gs[buf][2 * b], gd = gs[buf][2 * b + 1];
         const float u = beta * (vv - gd * dk);
-        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
         for (int e = 0; e < MS_PER; e += 4) {
           S[e] = fmaf(kk[e], u, gd * S[e]);
           S[e + 1] = fmaf(kk[e + 1], u, gd * S[e + 1]);
           S[e + 2] = fmaf(kk[e + 2], u, gd * S[e + 2]);
           S[e + 3] = fmaf(kk[e + 3], u, gd * S[e + 3]);
-          o0 = fmaf(S[e], qr[e * L], o0);
-          o1 = fmaf(S[e + 1], qr[(e + 1) * L], o1);
-          o2 = fmaf(S[e + 2], qr[(e + 2) * L], o2);
-          o3 = fmaf(S[e + 3], qr[(e + 3) * L], o3);
+          o0 = fmaf(S[e], qq[e], o0);
+          o1 = fmaf(S[e + 1], qq[e + 1], o1);
+          o2 = fmaf(S[e + 2], qq[e + 2], o2);
+          o3 = fmaf(S[e + 3], qq[e + 3], o3);
         }
-        o = (o0 + o1) + (o2 + o3);
       } else {
-        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+        const float hb = b < nb ? hd : 1.0f;
 #pragma unroll
         for (int e = 0; e < MS_PER; e += 4) {
-          S[e] = fmaf(kk[e], vv, hd * S[e]);
-          S[e + 1] = fmaf(kk[e + 1], vv, hd * S[e + 1]);
-          S[e + 2] = fmaf(kk[e + 2], vv, hd * S[e + 2]);
-          S[e + 3] = fmaf(kk[e + 3], vv, hd * S[e + 3]);
-          o0 = fmaf(S[e], qr[e * L], o0);
-          o1 = fmaf(S[e + 1], qr[(e + 1) * L], o1);
-          o2 = fmaf(S[e + 2], qr[(e + 2) * L], o2);
-          o3 = fmaf(S[e + 3], qr[(e + 3) * L], o3);
+          S[e] = fmaf(kk[e], vv, hb * S[e]);
+          S[e + 1] = fmaf(kk[e + 1], vv, hb * S[e + 1]);
+          S[e + 2] = fmaf(kk[e + 2], vv, hb * S[e + 2]);
+          S[e + 3] = fmaf(kk[e + 3], vv, hb * S[e + 3]);
+          o0 = fmaf(S[e], qq[e], o0);
+          o1 = fmaf(S[e + 1], qq[e + 1], o1);
+          o2 = fmaf(S[e + 2], qq[e + 2], o2);
+          o3 = fmaf(S[e + 3], qq[e + 3], o3);
         }
-        o = (o0 + o1) + (o2 + o3);
       }
+      float o = (o0 + o1) + (o2 + o3);
 #pragma unroll
       for (int m = 1; m < L; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-      if (on && sub == 0) p.out[(size_t)(tb + b) * p.out_stride + (size_t)h * p.V + col] = o;
+      // (a store the compiler knows to be global: behind a plain store through the argument's pointer,
+      // which might point anywhere, it would not start the next token's shared-memory loads early)
+      if (on && sub == 0 && b < nb)
+        asm volatile("st.global.f32 [%0], %1;" ::"l"(out_row + (size_t)(tb + b) * p.out_stride), "f"(o));
+    };
+    // eight tokens at a time without a loop between them (a token's read-out then runs under the next
+    // token's update), the rest of a short batch one by one
+    int b0 = 0;
+    for (; b0 + MS_UNROLL <= nb; b0 += MS_UNROLL) {
+#pragma unroll
+      for (int b = 0; b < MS_UNROLL; b++) token(b0 + b);
     }
+    for (; b0 < nb; b0++) token(b0);
   }
 #pragma unroll
   for (int e = 0; e < MS_PER; e++) {
-    const int i = e * L + sub;
+    const int i = sub * MS_PER + e;
     if (on && i < p.D) sp[(size_t)i * p.V + col] = S[e];
   }
 }
 
-template <int MODE>
-static int ms_launch(const MsArgs& p, int L, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
+template <int PER, int MODE, int NW>
+static int ms_launch(const MsArgs& p, int L, dim3 grid, cudaStream_t stream) {
+#define MS_CASE(LL)                                                                                         \
+  case LL:                                                                                                  \
+    if constexpr (PER == 16 ? PER * LL <= MS_MAX_DIM : PER * LL == 64)                                \
+      return sglc_launch(matrix_state_kernel<PER, LL, NW, MODE>, grid, dim3(32 * NW), 0, stream, 1, true, p); \
+    break;
   switch (L) {
-    case 1: return sglc_launch(matrix_state_kernel<1, MODE>, grid, dim3(threads), smem, stream, 1, true, p);
-    case 2: return sglc_launch(matrix_state_kernel<2, MODE>, grid, dim3(threads), smem, stream, 1, true, p);
-    case 4: return sglc_launch(matrix_state_kernel<4, MODE>, grid, dim3(threads), smem, stream, 1, true, p);
-    case 8: return sglc_launch(matrix_state_kernel<8, MODE>, grid, dim3(threads), smem, stream, 1, true, p);
+    MS_CASE(1) MS_CASE(2) MS_CASE(4) MS_CASE(8) MS_CASE(16) MS_CASE(32)
   }
+#undef MS_CASE
   return SGLC_ERR_UNSUPPORTED;
 }
+
+// Tuning hook: 0 (default) lets the launcher choose the entries a lane keeps; 8 or 16 fixes them where legal.
+static int g_ms_per = 0;
+SGLC_API void sglc_matrix_state_set_per(int per) { g_ms_per = per; }
 
 // mode 0: decay form (head_decay [H]); mode 1: gated delta rule (gates [T][2H]: beta, decay).
 // q, k: float rows with G heads of D; v: H heads of V; out: [T][H*V] float; state [n_slots][H][D][V].
@@ -175,28 +236,40 @@ SGLC_API int sglc_matrix_state(int mode, const float* q, long long q_stride, con
                                int D, int V, int silu_in, int* err, cudaStream_t stream) {
   if (R <= 0) return SGLC_OK;
   if (H <= 0 || G <= 0 || H % G != 0 || D <= 0 || V <= 0) return SGLC_ERR_ARGUMENT;
-  if (D > MS_PER * 8 || H > 65535) return SGLC_ERR_UNSUPPORTED;
-  int L = 1;
-  while (MS_PER * L < D) L <<= 1;
+  if (D > MS_MAX_DIM || H > 65535) return SGLC_ERR_UNSUPPORTED;
   MsArgs p = {};
   p.q = q; p.q_stride = q_stride; p.k = k; p.k_stride = k_stride; p.v = v; p.v_stride = v_stride;
   p.gates = gates; p.gates_stride = gates_stride; p.head_decay = head_decay;
   p.out = out; p.out_stride = out_stride; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
   p.R = R; p.H = H; p.G = G; p.D = D; p.V = V; p.n_slots = n_slots; p.silu_in = silu_in; p.err = err;
-  // a warp's worth of columns a block (the fewer columns, the more blocks share a request's tokens)
-  p.cols = V < 32 / L ? V : 32 / L;
-  const int threads = ((p.cols * L + 31) / 32) * 32;
-  const int zb = (V + p.cols - 1) / p.cols;
+  // Entries a lane keeps: 8 for key sizes of 33..64 while the warps still find a scheduler each (two
+  // on each of the 148 x 4); else 16.
+  auto lanes = [&](int per) { int l = 1; while (per * l < D) l <<= 1; return l; };
+  auto warps = [&](int per) { const int wc = 32 / lanes(per); return (long long)R * H * ((V + wc - 1) / wc); };
+  int per = 16;
+  for (int cand : {8}) {
+    const bool legal = cand * lanes(cand) == 64;      // (the kernels that exist)
+    if (legal && (g_ms_per == cand || (g_ms_per == 0 && warps(cand) <= 148LL * 4 * 2))) { per = cand; break; }
+  }
+  const int L = lanes(per);
+  // a warp takes 32 / L columns; four warps a block where a head has columns for more than one
+  const int wcols = 32 / L;
+  const int NW = V > wcols ? 4 : 1;
+  const int zb = (V + wcols * NW - 1) / (wcols * NW);
   if (zb > 65535) return SGLC_ERR_UNSUPPORTED;
-  const size_t smem = ((size_t)2 * MS_BATCH * MS_PER * L + (size_t)MS_BATCH * p.cols + 2 * MS_BATCH) * sizeof(float);
   const dim3 grid(R, H, zb);
+#define MS_GO(MODE)                                                                                   \
+  do {                                                                                                \
+    if (per == 8) return NW == 4 ? ms_launch<8, MODE, 4>(p, L, grid, stream) : ms_launch<8, MODE, 1>(p, L, grid, stream);   \
+    return NW == 4 ? ms_launch<16, MODE, 4>(p, L, grid, stream) : ms_launch<16, MODE, 1>(p, L, grid, stream);               \
+  } while (0)
   if (mode == MS_DECAY) {
     if (!head_decay) return SGLC_ERR_ARGUMENT;
-    return ms_launch<MS_DECAY>(p, L, grid, threads, smem, stream);
+    MS_GO(MS_DECAY);
   }
   if (mode == MS_DELTA) {
     if (!gates) return SGLC_ERR_ARGUMENT;
-    return ms_launch<MS_DELTA>(p, L, grid, threads, smem, stream);
+    MS_GO(MS_DELTA);
   }
   return SGLC_ERR_ARGUMENT;
 }

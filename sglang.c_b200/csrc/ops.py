@@ -617,12 +617,13 @@ def attention_prefill_tc_supported(q, cache, scale):
 
 
 def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, scale, window,
-                         n_requests, max_q_len, skip_single=False, kv_shared=False):
+                         n_requests, max_q_len, skip_single=False, kv_shared=False, chunk=None, sinks=None):
     """Causal attention of prompt portions on the tensor cores (tcgen05), bfloat16, head
     sizes 64 and 128.  q_start int32 [R+1], kv_len int32 [R] (lengths after this step).
     kv_shared: cache is [n_pages, 1, n_kv_heads, page_size, head_dim], rows that are keys and
-    values at once."""
-    _need_cuda(q, cache, block_table, q_start, kv_len, out)
+    values at once.  chunk: a query sees only the keys of its own chunk of so many positions;
+    sinks: float32 [n_heads], a score per head that joins the softmax's denominator."""
+    _need_cuda(q, cache, block_table, q_start, kv_len, out, sinks)
     for t, nm in ((block_table, "block_table"), (q_start, "q_start"), (kv_len, "kv_len")):
         _i32(t, nm)
     n_pages, two, Hkv, page_size, D = cache.shape
@@ -636,6 +637,17 @@ def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, s
         raise KernelError(f"attention_prefill_tc: cache {tuple(cache.shape)} does not fit kv_shared={kv_shared}")
     lib = build.load("attention_prefill_tc")
     err = _tc_buffers(q.device)[2]
+    if chunk or sinks is not None:
+        if kv_shared or (sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads)):
+            raise KernelError("attention_prefill_tc: a chunk mask or sinks go with separate keys and values; "
+                              "one float32 sink per head")
+        code = lib.sglc_attention_prefill_tc_ext(
+            _ptr(q), q.stride(0), _ptr(cache), _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(kv_len),
+            _ptr(out), out.stride(0), int(n_requests), int(max_q_len), n_heads, Hkv, D, page_size,
+            ctypes.c_float(scale), int(window or 0), int(chunk or 0), _ptr(sinks), q.shape[0], n_pages,
+            1 if skip_single else 0, _ptr(err), _stream())
+        _check(lib, code, f"attention_prefill_tc (head_dim {D}, chunk {chunk})")
+        return
     fn = lib.sglc_attention_prefill_tc_shared if kv_shared else lib.sglc_attention_prefill_tc
     code = fn(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
               block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(out),
@@ -850,7 +862,7 @@ def short_conv(x, taps, tail, y, token_req, q_start, state_slots, n_requests, se
                                len(segments), gh, int(bcol), int(acol), _ptr(a_log), _ptr(dt_bias), _ptr(gout),
                                ctypes.c_longlong(gout.stride(0) if gout is not None else 0),
                                _ptr(tc_error_flag(x.device)), _stream())
-    _check(lib, code, f"short_conv (channels {C}, taps {K})", n_kernels=2 if K > 1 else 1)
+    _check(lib, code, f"short_conv (channels {C}, taps {K})", n_kernels=2 if K > 1 and T != int(n_requests) else 1)
 
 
 MATRIX_STATE_MAX_DIM = 256

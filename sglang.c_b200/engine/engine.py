@@ -52,8 +52,9 @@ class Engine:
         # a block table never has more entries than the model has positions, nor than the pool has pages
         self.b_cap = min((plan.max_positions + self.page_size - 1) // self.page_size, self.cache.n_pages)
         self._paged = self.cache.paged_groups()
-        self._any_window = any(self.cache.groups[gi].need.window is not None or self.cache.groups[gi].need.chunk is not None
-                               for gi in self._paged)
+        # (a chunked group needs no such care: what it gives back lies before the chunk of the request's
+        # last position, which no later query sees, and it gives it back whenever a page is next taken)
+        self._any_window = any(self.cache.groups[gi].need.window is not None for gi in self._paged)
         self._rep = None                  # what a repeated step of single tokens updates in place
         self._poisoned = set()            # requests a failed step left with positions never computed
         self._prepared = None             # prepare_repeat's mark: indices of requests that took a page

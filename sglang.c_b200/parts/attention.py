@@ -243,6 +243,15 @@ class RotaryAttention(Part):
                       self.rotary.multiplier, self.rotary.dims, float(p["eps"]) if p.get("qk_norm") else None, q,
                       cache.tensor, grp.slots, H, G, D, V, grp.page_size)
         o = ctx.alloc((T, H * V), self.rt.act_dtype)
+        # a step of prompt portions only, keys and values of one size the tensor-core kernel takes (a
+        # page is then its [2][G][page_size][D]): 128-query tiles on the tensor cores; every other
+        # step (single tokens among them, other sizes, 32-bit) goes to the general kernel
+        if D == V and ctx.n_decode == 0 and ctx.max_q_len > 1 and self.rt.dtype == "bfloat16":
+            pages = cache.tensor.view(cache.tensor.shape[0], 2, G, grp.page_size, D)
+            if ops.attention_prefill_tc_supported(q, pages, float(p["scale"])) and o.stride(0) % 8 == 0:
+                ops.attention_prefill_tc(q, pages, grp.block_table, ctx.q_start, ctx.kv_len, o, H, float(p["scale"]),
+                                         p.get("window"), ctx.R, ctx.max_q_len, chunk=p.get("chunk"), sinks=self.sink)
+                return self.out.forward(ctx, o, out=out, residual=residual)
         ops.attention_ext(q, cache.tensor, grp.block_table, ctx.token_req, ctx.positions, o, H, G, D, V, grp.page_size,
                           float(p["scale"]), p.get("window"), p.get("chunk"), self.sink, ctx.max_keys,
                           max_q_len=ctx.max_q_len)

@@ -274,6 +274,56 @@ def test_rotary_attention_chunk_edges_sinks_and_page_borders(dtype, H, G, D, V, 
         assert np.abs(out.float().cpu().numpy() - want).max() < tol, first
 
 
+@pytest.mark.parametrize("D,chunk,G", [(64, 24, 1), (64, 128, 2), (128, 200, 2), (64, 1000, 1)])
+def test_tensor_core_prefill_attention_with_chunks_and_sinks(D, chunk, G):
+    """The tensor-core prompt kernel's form with a chunk mask and sinks: chunks that end inside a tile
+    of 128 keys, that span tiles, that are longer than the prompt; prompts whole, and in two portions
+    the second of which begins inside a chunk and inside a tile; a short request beside the long one."""
+    from sglang_c_b200.csrc import ops
+    from sglang_c_b200.parts.registry import get_part
+    rng = np.random.default_rng(D + chunk)
+    H, V, E, page = 2 * G, D, 24, 16
+    lens = [333, 70]
+    m = {"heads": H, "kv_heads": G, "dim": D, "vdim": V, "scale": 2.0 / math.sqrt(D), "mask": {"size": chunk},
+         "rot": {"dims": D // 2, "base": 10000.0}}
+    w = {"q": rng.standard_normal((H * D, E)), "k": rng.standard_normal((G * D, E)), "v": rng.standard_normal((G * V, E)),
+         "o": np.eye(H * V), "sink": rng.standard_normal(H) * 2 + 2}
+    hs = [dev(rng.standard_normal((n, E)), torch.bfloat16).float().cpu().numpy().astype(np.float64) for n in lens]
+    want = [P.chunked_sink_attention(h, w, "", m, 1e-6) for h in hs]
+    no_sink = P.chunked_sink_attention(hs[0], dict(w, sink=np.full(H, -1e9)), "", m, 1e-6)
+    assert np.abs(no_sink - want[0]).max() > 0.05 * np.abs(want[0]).max()
+    rot = get_part("position", "rotary")(m["rot"], None)
+    rot.load({}, None)
+    freq = rot.frequencies.to(DEV)
+    blocks = [(n + page - 1) // page for n in lens]
+    n_pages = sum(blocks) + 2
+    perm = rng.permutation(n_pages)
+    tables = np.zeros((2, max(blocks)), dtype=np.int64)
+    tables[0, :blocks[0]], tables[1, :blocks[1]] = perm[:blocks[0]], perm[blocks[0]:blocks[0] + blocks[1]]
+    xs = [dev(np.concatenate([h @ w["q"].T, h @ w["k"].T, h @ w["v"].T], 1)) for h in hs]
+    for cuts in ([(0, 333), (0, 70)],), ([(0, 141), (0, 9)], [(141, 333), (9, 70)]):
+        cache = torch.zeros((n_pages, G * page * (D + V)), dtype=torch.bfloat16, device=DEV)
+        got = [np.zeros_like(x) for x in want]
+        for step in cuts:
+            x = torch.cat([xs[r][lo:hi] for r, (lo, hi) in enumerate(step)])
+            pos = np.concatenate([np.arange(lo, hi) for lo, hi in step])
+            slots = np.concatenate([tables[r][np.arange(lo, hi) // page] * page + np.arange(lo, hi) % page
+                                    for r, (lo, hi) in enumerate(step)])
+            T = len(pos)
+            q = torch.empty((T, H * D), dtype=torch.bfloat16, device=DEV)
+            ops.rotary_kv(x, i32(pos), freq, rot.multiplier, D // 2, 1e-6, q, cache, i32(slots), H, G, D, V, page)
+            out = torch.zeros((T, H * V), dtype=torch.bfloat16, device=DEV)
+            q_start = np.concatenate([[0], np.cumsum([hi - lo for lo, hi in step])])
+            ops.attention_prefill_tc(q, cache.view(n_pages, 2, G, page, D), i32(tables), i32(q_start),
+                                     i32([hi for _, hi in step]), out, H, m["scale"], None, 2, max(hi - lo for lo, hi in step),
+                                     chunk=chunk, sinks=dev(w["sink"]))
+            o = out.float().cpu().numpy()
+            for r, (lo, hi) in enumerate(step):
+                got[r][lo:hi] = o[q_start[r]:q_start[r + 1]]
+        for r in range(2):
+            assert np.abs(got[r] - want[r]).max() < 3e-2 * np.abs(want[r]).max(), (cuts, r)
+
+
 # ---------------------------------------------------------------------------- whole models
 def requests_for(name):
     V = ZUR[name]["vocab"]
