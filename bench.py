@@ -719,7 +719,7 @@ def zuretar_config(base, n_layer):
     hq = max(1, H // 4)
     par = {"left": {"heads": H, "kv_heads": hq, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 256},
                     "rot": {"base": 10000.0, "dims": 64,
-                            "scaling": {"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}}},
+                            "scaling": {"factor": 8.0, "original": 256, "fast": 16.0, "slow": 2.0}}},
            "right": {"heads": hq, "dim": 64, "vdim": 64, "decay": [1.0 - 2.0 ** -(3 + i % 6) for i in range(hq)]}}
     layers = []
     for i in range(n_layer):

@@ -134,17 +134,21 @@ matrix_state_kernel(MsArgs p) {
     stage(buf);
     __syncthreads();           // the batch is staged; everybody is done with the other half's last batch
     if (tb + MS_BATCH < t1) fetch(tb + MS_BATCH);
-    auto token = [&](int b) {
+    // a token's inputs out of shared memory into registers
+    auto take = [&](int b, float (&kk)[MS_PER], float (&qq)[MS_PER], float& vv, float& beta, float& gd) {
       const float4* kr = reinterpret_cast<const float4*>(ks[buf] + b * SP + sub * LP);
       const float4* qr = reinterpret_cast<const float4*>(qs[buf] + b * SP + sub * LP);
-      const float vv = vs[buf][b * COLS + lcol];
-      float kk[MS_PER], qq[MS_PER];
 #pragma unroll
       for (int e = 0; e < MS_PER; e += 4) {
         const float4 k4 = kr[e / 4], q4 = qr[e / 4];
         kk[e] = k4.x; kk[e + 1] = k4.y; kk[e + 2] = k4.z; kk[e + 3] = k4.w;
         qq[e] = q4.x; qq[e + 1] = q4.y; qq[e + 2] = q4.z; qq[e + 3] = q4.w;
       }
+      vv = vs[buf][b * COLS + lcol];
+      if (MODE == MS_DELTA) { beta = gs[buf][2 * b]; gd = gs[buf][2 * b + 1]; }
+    };
+    // the state's update by one token; returns this lane's share of the read-out
+    auto update = [&](const float (&kk)[MS_PER], const float (&qq)[MS_PER], float vv, float beta, float gd) {
       float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
       if (MODE == MS_DELTA) {
         float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
@@ -158,7 +162,6 @@ matrix_state_kernel(MsArgs p) {
         float dk = (d0 + d1) + (d2 + d3);
 #pragma unroll
         for (int m = 1; m < L; m <<= 1) dk += __shfl_xor_sync(0xffffffffu, dk, m);
-        const float beta = gs[buf][2 * b], gd = gs[buf][2 * b + 1];
         const float u = beta * (vv - gd * dk);
 #pragma unroll
         for (int e = 0; e < MS_PER; e += 4) {
@@ -172,35 +175,49 @@ matrix_state_kernel(MsArgs p) {
           o3 = fmaf(S[e + 3], qq[e + 3], o3);
         }
       } else {
-        const float hb = b < nb ? hd : 1.0f;
 #pragma unroll
         for (int e = 0; e < MS_PER; e += 4) {
-          S[e] = fmaf(kk[e], vv, hb * S[e]);
-          S[e + 1] = fmaf(kk[e + 1], vv, hb * S[e + 1]);
-          S[e + 2] = fmaf(kk[e + 2], vv, hb * S[e + 2]);
-          S[e + 3] = fmaf(kk[e + 3], vv, hb * S[e + 3]);
+          S[e] = fmaf(kk[e], vv, hd * S[e]);
+          S[e + 1] = fmaf(kk[e + 1], vv, hd * S[e + 1]);
+          S[e + 2] = fmaf(kk[e + 2], vv, hd * S[e + 2]);
+          S[e + 3] = fmaf(kk[e + 3], vv, hd * S[e + 3]);
           o0 = fmaf(S[e], qq[e], o0);
           o1 = fmaf(S[e + 1], qq[e + 1], o1);
           o2 = fmaf(S[e + 2], qq[e + 2], o2);
           o3 = fmaf(S[e + 3], qq[e + 3], o3);
         }
       }
-      float o = (o0 + o1) + (o2 + o3);
+      return (o0 + o1) + (o2 + o3);
+    };
+    // the read-out summed over the column's lanes and written (a store the compiler knows to be global)
+    auto finish = [&](int b, float o) {
 #pragma unroll
       for (int m = 1; m < L; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-      // (a store the compiler knows to be global: behind a plain store through the argument's pointer,
-      // which might point anywhere, it would not start the next token's shared-memory loads early)
-      if (on && sub == 0 && b < nb)
+      if (on && sub == 0)
         asm volatile("st.global.f32 [%0], %1;" ::"l"(out_row + (size_t)(tb + b) * p.out_stride), "f"(o));
     };
-    // eight tokens at a time without a loop between them (a token's read-out then runs under the next
-    // token's update), the rest of a short batch one by one
+    // Eight tokens at a time without a loop between them: a token's inputs leave shared memory while
+    // the token before is worked on, and the eight read-outs are summed over their lanes together
+    // behind the eight updates (what is left between two tokens' updates is the chain itself: the
+    // dot product, its sum over the lanes, the correction).  The rest of a short batch one by one.
     int b0 = 0;
     for (; b0 + MS_UNROLL <= nb; b0 += MS_UNROLL) {
+      float part[MS_UNROLL];
+      float kk[2][MS_PER], qq[2][MS_PER], vv[2], beta[2] = {0.0f, 0.0f}, gd[2] = {1.0f, 1.0f};
+      take(b0, kk[0], qq[0], vv[0], beta[0], gd[0]);
 #pragma unroll
-      for (int b = 0; b < MS_UNROLL; b++) token(b0 + b);
+      for (int b = 0; b < MS_UNROLL; b++) {
+        if (b + 1 < MS_UNROLL) take(b0 + b + 1, kk[(b + 1) & 1], qq[(b + 1) & 1], vv[(b + 1) & 1], beta[(b + 1) & 1], gd[(b + 1) & 1]);
+        part[b] = update(kk[b & 1], qq[b & 1], vv[b & 1], beta[b & 1], gd[b & 1]);
+      }
+#pragma unroll
+      for (int b = 0; b < MS_UNROLL; b++) finish(b0 + b, part[b]);
     }
-    for (; b0 < nb; b0++) token(b0);
+    for (; b0 < nb; b0++) {
+      float kk[MS_PER], qq[MS_PER], vv, beta = 0.0f, gd = 1.0f;
+      take(b0, kk, qq, vv, beta, gd);
+      finish(b0, update(kk, qq, vv, beta, gd));
+    }
   }
 #pragma unroll
   for (int e = 0; e < MS_PER; e++) {

@@ -192,7 +192,7 @@ def test_router_groups_correction_and_negative_choice_scores():
     rng = np.random.default_rng(11)
     T, E = 200, 12
     z = rng.standard_normal((T, E)) * 2
-    for groups, top, corr in (((3, 2), 4, rng.standard_normal(E) - 2.0), ((4, 1), 3, rng.standard_normal(E) * 0.3),
+    for groups, top, corr in (((4, 2), 5, rng.standard_normal(E) - 2.0), ((3, 1), 3, rng.standard_normal(E) * 0.3),
                               (None, 5, np.zeros(E)), ((12, 5), 2, rng.standard_normal(E)), ((2, 2), 12, -rng.random(E))):
         r = {"experts": E, "top": top}
         if groups:
