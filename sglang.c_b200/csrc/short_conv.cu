@@ -17,7 +17,7 @@
 
 SGLC_DEFINE_ERROR_STRING()
 
-constexpr int CONV_MAX_TAPS = 16;
+constexpr int CONV_MAX_TAPS = 256;
 constexpr int CONV_SEGS = 4;
 constexpr int CONV_WARPS = 4;
 
