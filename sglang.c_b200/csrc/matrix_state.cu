@@ -23,7 +23,7 @@
 
 SGLC_DEFINE_ERROR_STRING()
 
-constexpr int MS_UNROLL = 8;      // tokens worked on without a loop between them
+constexpr int MS_UNROLL = 4;      // tokens worked on without a loop between them
 constexpr int MS_MAX_DIM = 256;   // key sizes up to 16 entries a lane x 16 lanes
 
 enum { MS_DECAY = 0, MS_DELTA = 1 };
@@ -196,9 +196,10 @@ matrix_state_kernel(MsArgs p) {
       if (on && sub == 0)
         asm volatile("st.global.f32 [%0], %1;" ::"l"(out_row + (size_t)(tb + b) * p.out_stride), "f"(o));
     };
-    // Eight tokens at a time without a loop between them: a token's inputs leave shared memory while
-    // the token before is worked on, and the eight read-outs are summed over their lanes together
-    // behind the eight updates (what is left between two tokens' updates is the chain itself: the
+    // Four tokens at a time without a loop between them (eight were a tenth slower: the straight
+    // code outgrew what a scheduler keeps of its instructions): a token's inputs leave shared memory
+    // while the token before is worked on, and the four read-outs are summed over their lanes together
+    // behind the four updates (what is left between two tokens' updates is the chain itself: the
     // dot product, its sum over the lanes, the correction).  The rest of a short batch one by one.
     int b0 = 0;
     for (; b0 + MS_UNROLL <= nb; b0 += MS_UNROLL) {
